@@ -1,0 +1,197 @@
+#!/usr/bin/env python
+"""Headline benchmark: compressed AllReduce bus bandwidth on gradient-like data.
+
+    python bench.py --gpus N --steps K --warmup W            (N = 1)
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N \
+        --master-addr 127.0.0.1 --master-port P bench.py --gpus N --steps K --warmup W
+
+One "step" is one AllReduce(sum) of a 256 MiB bf16 buffer per rank (Laplace(0, 1e-3)
+values with 0.1 % of the entries multiplied by 100), compressed to int8 with one
+absmax/127 scale per 128 values, done by ONE fused kernel per rank (two-shot over
+NVSwitch peer memory). The reported value is nccl-tests bus bandwidth
+(algbw * 2(n-1)/n, algbw = message bytes / time) with the time taken on the device
+and the maximum over ranks; at N = 1 there is no bus, so the value is algbw of the
+local quantise/dequantise round trip the kernel still performs.
+
+`--impl reference` runs the reference's own allreduce benchmark binary under its own
+int8 wrapper (built unmodified from baseline/_ref) and prints the same line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bytes", type=int, default=256 << 20, help="message bytes per rank")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "f16"])
+    ap.add_argument("--codec", default="int8", choices=["int8", "fp8", "none", "int8_g256"])
+    ap.add_argument("--algo", default="twoshot", choices=["auto", "twoshot", "oneshot", "ring", "tree", "nvls"])
+    ap.add_argument("--error-feedback", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        from baseline.run_reference import main as ref_main
+
+        return ref_main(args)
+
+    import torch
+    import torch.distributed as dist
+
+    from ccbench_b200 import Communicator
+    from ccbench_b200.comm import launch_count
+    from ccbench_b200.models.workloads import gradient_like
+    from ccbench_b200.ops.codecs import wire_ratio
+    from ccbench_b200.utils.clocks import ClockSampler
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        comm = Communicator.from_torch_distributed(nvls=(args.algo == "nvls"))
+    else:
+        comm = Communicator.create(0, 1, f"bench{os.getpid()}")
+
+    dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[args.dtype]
+    count = args.bytes // torch.empty((), dtype=dtype).element_size()
+    x = gradient_like(count, dtype, seed=rank, device=dev)
+    y = torch.empty_like(x)
+    ef = torch.zeros(count, device=dev) if args.error_feedback else None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        comm.all_reduce(x, y, codec=args.codec, algo=args.algo, error_feedback=ef)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    rc, words = comm.status()
+    if rc != 0:
+        raise SystemExit(f"communicator error during warm-up: {words}")
+
+    # ---- device-timed region -------------------------------------------------
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = launch_count()
+    with ClockSampler(local_rank, 100) as clk:
+        barrier()
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        barrier()
+    launches = launch_count() - l0
+    ms = start.elapsed_time(stop)
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = t.item() / args.steps
+    clocks = clk.summary()
+
+    # ---- accuracy of the last result against the exact fp32 sum ----------------
+    exact = x.float()
+    if world > 1:
+        dist.all_reduce(exact)
+    rel_l2 = ((y.float() - exact).norm() / exact.norm()).item()
+    del exact
+
+    # ---- end to end: pinned host input -> H2D -> AllReduce -> D2H of a sample ----
+    e2e = None
+    if not args.no_e2e:
+        hx = torch.empty(count, dtype=dtype).pin_memory()
+        hx.copy_(x)
+        sample = 16384
+        hy = torch.empty(sample, dtype=dtype).pin_memory()
+        copy_stream = torch.cuda.Stream()
+        xin = [torch.empty_like(x), torch.empty_like(x)]
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        freed = [torch.cuda.Event(), torch.cuda.Event()]
+
+        def e2e_loop(k):
+            # step i's input upload overlaps step i-1's collective (two device buffers)
+            with torch.cuda.stream(copy_stream):
+                xin[0].copy_(hx, non_blocking=True)
+                ready[0].record()
+            for i in range(k):
+                cur, nxt = i & 1, (i + 1) & 1
+                if i + 1 < k:
+                    with torch.cuda.stream(copy_stream):
+                        if i >= 1:
+                            copy_stream.wait_event(freed[nxt])
+                        xin[nxt].copy_(hx, non_blocking=True)
+                        ready[nxt].record()
+                torch.cuda.current_stream().wait_event(ready[cur])
+                comm.all_reduce(xin[cur], y, codec=args.codec, algo=args.algo, error_feedback=ef)
+                freed[cur].record()
+                hy.copy_(y[:sample], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+
+        e2e_loop(2)
+        barrier()
+        es, ee = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        es.record()
+        t0 = time.perf_counter()
+        e2e_loop(args.steps)
+        ee.record()
+        barrier()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        te = torch.tensor([max(es.elapsed_time(ee), 0.0)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e_ms = te.item() / args.steps
+        factor = 2 * (world - 1) / world if world > 1 else 1.0
+        e2e = {"value": args.bytes / (e_ms * 1e-3) / 1e9 * factor, "unit": "GB/s",
+               "ms_per_step": e_ms, "wall_ms_per_step": wall_ms / args.steps,
+               "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": sample * hy.element_size()}
+
+    factor = 2 * (world - 1) / world if world > 1 else 1.0
+    algbw = args.bytes / (ms_per_step * 1e-3) / 1e9
+    if rank == 0:
+        line = {
+            "metric": "compressed_allreduce_busbw" if world > 1 else "compressed_allreduce_algbw_single_gpu",
+            "value": algbw * factor, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+            "impl": "ours",
+            "config": {"model": "gradient-like buffer: Laplace(0,1e-3) + 0.1% x100 outliers",
+                       "global_batch": args.bytes * world, "seq_len": count,
+                       "message_bytes_per_rank": args.bytes, "codec": args.codec, "algo": args.algo,
+                       "error_feedback": bool(args.error_feedback),
+                       "parallelism": f"dp{world}", "l2": "inputs (256 MiB) larger than L2, no flush needed",
+                       "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},
+            "algbw": algbw, "ref_definition_bw": 2 * algbw, "compression_ratio": wire_ratio(args.codec, dtype),
+            "rel_l2_error": rel_l2, "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+            "e2e": e2e, "gpu_launches": launches,
+        }
+        print(json.dumps(line), flush=True)
+    comm.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,232 @@
+"""Communicator: the Python face of libccb.so.
+
+One `Communicator` per process and GPU (`Communicator.from_torch_distributed`) or one
+that plays all ranks on a single GPU inside one cooperative launch
+(`Communicator.local`, for boxes with fewer GPUs than ranks). Every method is one
+fused kernel launch on the current torch CUDA stream.
+
+The reference exposes these collectives only as interposed `nccl*` symbols
+(userconfig/wrapper_code_examples/communication/plain_nccl_compress/
+plain_nccl_compress.cu:654-1147); the interposer of this repository calls the same C
+entry points that this class wraps.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import uuid
+from typing import Optional, Sequence, Union
+
+import torch
+
+from . import constants as K
+from ._lib import lib
+
+Tensors = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+_DTYPES = {torch.float32: K.F32, torch.bfloat16: K.BF16, torch.float16: K.F16}
+
+
+class CcbError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"ccb error {code}: {msg}")
+        self.code = code
+
+
+def _code(x, table) -> int:
+    return table[x] if isinstance(x, str) else int(x)
+
+
+class Communicator:
+    def __init__(self, handle: int, device: torch.device):
+        self._h = ctypes.c_void_p(handle)
+        self.device = device
+        L = lib()
+        self.rank = L.ccb_comm_rank(self._h)
+        self.nranks = L.ccb_comm_nranks(self._h)
+        self.nlocal = L.ccb_comm_nlocal(self._h)
+
+    # ------------------------------------------------------------ creation --
+    @classmethod
+    def local(cls, nranks: int, arena_bytes: int = 0, device: Optional[torch.device] = None) -> "Communicator":
+        """All `nranks` ranks on one GPU; every call takes one tensor per rank."""
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        with torch.cuda.device(device):
+            h = ctypes.c_void_p()
+            rc = lib().ccb_comm_create_local(ctypes.byref(h), nranks, arena_bytes)
+        _check(rc)
+        return cls(h.value, device)
+
+    @classmethod
+    def create(cls, rank: int, nranks: int, tag: str, arena_bytes: int = 0, nvls: bool = False,
+               device: Optional[torch.device] = None) -> "Communicator":
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        with torch.cuda.device(device):
+            torch.cuda.init()
+            h = ctypes.c_void_p()
+            rc = lib().ccb_comm_create(ctypes.byref(h), rank, nranks, tag.encode(), arena_bytes, 1 if nvls else 0)
+        _check(rc)
+        return cls(h.value, device)
+
+    @classmethod
+    def from_torch_distributed(cls, group=None, arena_bytes: int = 0, nvls: bool = False) -> "Communicator":
+        """Build over an initialised torch.distributed group; the group is used once,
+        to agree on a rendezvous tag."""
+        import torch.distributed as dist
+
+        rank, n = dist.get_rank(group), dist.get_world_size(group)
+        tag = [uuid.uuid4().hex[:16] if rank == 0 else None]
+        dist.broadcast_object_list(tag, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        return cls.create(rank, n, tag[0], arena_bytes, nvls)
+
+    def close(self) -> None:
+        if self._h:
+            lib().ccb_comm_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------- helpers --
+    @property
+    def has_nvls(self) -> bool:
+        return bool(lib().ccb_comm_has_nvls(self._h))
+
+    @property
+    def arena_bytes(self) -> int:
+        return int(lib().ccb_comm_arena_bytes(self._h))
+
+    def set_timeout_ms(self, ms: int) -> None:
+        _check(lib().ccb_comm_set_timeout_ms(self._h, ms))
+
+    def set_max_ctas(self, ctas: int) -> None:
+        _check(lib().ccb_comm_set_max_ctas(self._h, ctas))
+
+    def status(self) -> tuple[int, list[int]]:
+        words = (ctypes.c_uint32 * 8)()
+        rc = lib().ccb_comm_status(self._h, words)
+        return rc, list(words)
+
+    def _ptrs(self, t: Optional[Tensors], name: str):
+        if t is None:
+            return None, None
+        ts = [t] if isinstance(t, torch.Tensor) else list(t)
+        if len(ts) != self.nlocal:
+            raise ValueError(f"{name}: expected {self.nlocal} tensor(s), got {len(ts)}")
+        for x in ts:
+            if not x.is_cuda or not x.is_contiguous():
+                raise ValueError(f"{name}: tensors must be contiguous CUDA tensors")
+        arr = (ctypes.c_void_p * self.nlocal)(*[x.data_ptr() for x in ts])
+        return arr, ts
+
+    @staticmethod
+    def _stream() -> ctypes.c_void_p:
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    @staticmethod
+    def _dtype(ts) -> int:
+        dt = ts[0].dtype
+        if dt not in _DTYPES:
+            raise TypeError(f"unsupported dtype {dt}; use float32, bfloat16 or float16")
+        return _DTYPES[dt]
+
+    # --------------------------------------------------------- collectives --
+    def all_reduce(self, send: Tensors, recv: Optional[Tensors] = None, *, op="sum", codec="int8", algo="auto",
+                   error_feedback: Optional[Tensors] = None):
+        """recv = sum over ranks of send, moved over the wire in `codec`. In place when
+        recv is None. `error_feedback` is one fp32 tensor per rank of the same element
+        count that carries the quantisation residual from call to call."""
+        recv = send if recv is None else recv
+        sp, st = self._ptrs(send, "send")
+        rp, rt = self._ptrs(recv, "recv")
+        ep, et = self._ptrs(error_feedback, "error_feedback")
+        if et is not None and any(e.dtype != torch.float32 or e.numel() != st[0].numel() for e in et):
+            raise ValueError("error_feedback must be float32 with send's element count")
+        _check(lib().ccb_all_reduce(self._h, sp, rp, st[0].numel(), self._dtype(st), _code(op, K.OPS),
+                                    _code(codec, K.CODECS), _code(algo, K.ALGOS), ep, self._stream()))
+        return recv
+
+    def reduce_scatter(self, send: Tensors, recv: Tensors, *, op="sum", codec="int8",
+                       error_feedback: Optional[Tensors] = None):
+        sp, st = self._ptrs(send, "send")
+        rp, rt = self._ptrs(recv, "recv")
+        ep, _ = self._ptrs(error_feedback, "error_feedback")
+        if st[0].numel() != rt[0].numel() * self.nranks:
+            raise ValueError("send must hold nranks * recv.numel() elements")
+        _check(lib().ccb_reduce_scatter(self._h, sp, rp, rt[0].numel(), self._dtype(st), _code(op, K.OPS),
+                                        _code(codec, K.CODECS), ep, self._stream()))
+        return recv
+
+    def reduce(self, send: Tensors, recv: Tensors, root: int = 0, *, op="sum", codec="int8"):
+        sp, st = self._ptrs(send, "send")
+        rp, _ = self._ptrs(recv, "recv")
+        _check(lib().ccb_reduce(self._h, sp, rp, st[0].numel(), self._dtype(st), _code(op, K.OPS), root,
+                                _code(codec, K.CODECS), self._stream()))
+        return recv
+
+    def all_gather(self, send: Tensors, recv: Tensors, *, codec="int8"):
+        sp, st = self._ptrs(send, "send")
+        rp, rt = self._ptrs(recv, "recv")
+        if rt[0].numel() != st[0].numel() * self.nranks:
+            raise ValueError("recv must hold nranks * send.numel() elements")
+        _check(lib().ccb_all_gather(self._h, sp, rp, st[0].numel(), self._dtype(st), _code(codec, K.CODECS),
+                                    self._stream()))
+        return recv
+
+    def broadcast(self, send: Tensors, recv: Optional[Tensors] = None, root: int = 0, *, codec="int8"):
+        recv = send if recv is None else recv
+        sp, st = self._ptrs(send, "send")
+        rp, _ = self._ptrs(recv, "recv")
+        _check(lib().ccb_broadcast(self._h, sp, rp, st[0].numel(), self._dtype(st), root, _code(codec, K.CODECS),
+                                   self._stream()))
+        return recv
+
+    def all_to_all(self, send: Tensors, recv: Tensors, *, codec="fp8"):
+        sp, st = self._ptrs(send, "send")
+        rp, _ = self._ptrs(recv, "recv")
+        if st[0].numel() % self.nranks:
+            raise ValueError("send.numel() must be a multiple of nranks")
+        _check(lib().ccb_all_to_all(self._h, sp, rp, st[0].numel() // self.nranks, self._dtype(st),
+                                    _code(codec, K.CODECS), self._stream()))
+        return recv
+
+    def scatter(self, send: Tensors, recv: Tensors, root: int = 0, *, codec="none"):
+        sp, _ = self._ptrs(send, "send")
+        rp, rt = self._ptrs(recv, "recv")
+        _check(lib().ccb_scatter(self._h, sp, rp, rt[0].numel(), self._dtype(rt), root, _code(codec, K.CODECS),
+                                 self._stream()))
+        return recv
+
+    def gather(self, send: Tensors, recv: Tensors, root: int = 0, *, codec="none"):
+        sp, st = self._ptrs(send, "send")
+        rp, _ = self._ptrs(recv, "recv")
+        _check(lib().ccb_gather(self._h, sp, rp, st[0].numel(), self._dtype(st), root, _code(codec, K.CODECS),
+                                self._stream()))
+        return recv
+
+    def exchange(self, send: Tensors, recv: Tensors, counts, send_offsets, recv_offsets, *, codec="none"):
+        """General alltoallv: counts[src][dst] elements from send(src)+send_offsets[src][dst]
+        to recv(dst)+recv_offsets[dst][src]. Covers AllGatherv / Scatterv."""
+        n = self.nranks
+        sp, st = self._ptrs(send, "send")
+        rp, _ = self._ptrs(recv, "recv")
+        flat = lambda m: (ctypes.c_uint64 * (n * n))(*[int(m[i][j]) for i in range(n) for j in range(n)])
+        _check(lib().ccb_exchange(self._h, sp, rp, flat(counts), flat(send_offsets), flat(recv_offsets),
+                                  self._dtype(st), _code(codec, K.CODECS), self._stream()))
+        return recv
+
+
+def _check(rc: int) -> None:
+    if rc != K.OK:
+        raise CcbError(rc, (lib().ccb_last_error() or b"").decode(errors="replace"))
+
+
+def wire_bytes(codec, dtype: torch.dtype, count: int) -> int:
+    return int(lib().ccb_wire_bytes(_code(codec, K.CODECS), _DTYPES[dtype], count))
+
+
+def launch_count() -> int:
+    return int(lib().ccb_launch_count())

@@ -1,0 +1,171 @@
+// Wire codecs used inside the fused collective kernels. A codec turns the 16 fp32
+// values a lane holds into a Packet (payload registers + block scale) and back;
+// `store`/`load` move a Packet to/from a wire slot laid out as
+//     [payload: pad elements][scales: pad / kGroup entries]
+// where `pad` (a multiple of 512) is the slot's element extent. `encode` is
+// warp-collective (lanes of one quantisation group share an absmax by shuffle), so
+// every lane of a warp must call it together.
+//
+//   CodecNone<T>   elements travel as T (exact for T, used for the uncompressed paths)
+//   CodecInt8<G>   int8, fp32 scale = absmax/127 per G values (G = 128 or 256)
+//   CodecFp8       fp8 e4m3, ue8m0 (power-of-two) scale byte per 32 values
+//
+// The reference's only GPU codec is int8 with a per-group reciprocal scale
+// (userconfig/wrapper_code_examples/communication/plain_nccl_compress/
+// plain_nccl_compress.cu:141-191), run as separate quantize / dequantize kernels
+// around ncclSend / ncclRecv; here the codec lives in registers of the kernel that
+// also moves the bytes.
+#pragma once
+#include <cuda_fp8.h>
+
+#include "ccb_device.cuh"
+
+namespace ccb {
+
+template <class T>
+struct CodecNone {
+  static constexpr int kId = CCB_CODEC_NONE;
+  static constexpr int kQ = sizeof(T);  // uint4 registers per lane
+  struct Packet { uint4 q[kQ]; };
+  static __host__ __device__ size_t slot_bytes(size_t pad) { return pad * sizeof(T); }
+  static __device__ __forceinline__ void encode(const float (&v)[16], Packet& pk) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        pk.q[k] = make_uint4(__float_as_uint(v[4 * k]), __float_as_uint(v[4 * k + 1]),
+                             __float_as_uint(v[4 * k + 2]), __float_as_uint(v[4 * k + 3]));
+    } else {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        T* h = reinterpret_cast<T*>(&pk.q[k]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = Elem<T>::from_f(v[8 * k + i]);
+      }
+    }
+  }
+  static __device__ __forceinline__ void decode(const Packet& pk, float (&v)[16]) {
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[4 * k] = __uint_as_float(pk.q[k].x); v[4 * k + 1] = __uint_as_float(pk.q[k].y);
+        v[4 * k + 2] = __uint_as_float(pk.q[k].z); v[4 * k + 3] = __uint_as_float(pk.q[k].w);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const T* h = reinterpret_cast<const T*>(&pk.q[k]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[8 * k + i] = Elem<T>::to_f(h[i]);
+      }
+    }
+  }
+  static __device__ __forceinline__ void store(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    char* p = slot + idx * sizeof(T);
+#pragma unroll
+    for (int k = 0; k < kQ; ++k) stg(p + 16 * k, pk.q[k]);
+  }
+  static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
+    const char* p = slot + idx * sizeof(T);
+#pragma unroll
+    for (int k = 0; k < kQ; ++k) pk.q[k] = ldg_cg(p + 16 * k);
+  }
+};
+
+__device__ __forceinline__ float absmax16(const float (&v)[16]) {
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
+
+template <int G>
+struct CodecInt8 {
+  static_assert(G == 128 || G == 256, "group must be 128 or 256");
+  static constexpr int kId = (G == 128) ? CCB_CODEC_INT8 : CCB_CODEC_INT8_G256;
+  static constexpr int kLanes = G / 16;  // lanes sharing one scale
+  struct Packet { uint4 q; float scale; };
+  static __host__ __device__ size_t slot_bytes(size_t pad) { return pad + pad / G * 4; }
+  static __device__ __forceinline__ void encode(const float (&v)[16], Packet& pk) {
+    float m = absmax16(v);
+#pragma unroll
+    for (int d = 1; d < kLanes; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    const float inv = m > 0.f ? 127.f / m : 0.f;
+    pk.scale = m / 127.f;
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      int a = __float2int_rn(v[4 * k] * inv), b = __float2int_rn(v[4 * k + 1] * inv);
+      int c = __float2int_rn(v[4 * k + 2] * inv), d = __float2int_rn(v[4 * k + 3] * inv);
+      w[k] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+    }
+    pk.q = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ void decode(const Packet& pk, float (&v)[16]) {
+    const uint32_t w[4] = {pk.q.x, pk.q.y, pk.q.z, pk.q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * k + i] = (float)(int)(int8_t)(w[k] >> (8 * i)) * pk.scale;
+    }
+  }
+  static __device__ __forceinline__ void store(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    stg(slot + idx, pk.q);
+    if ((threadIdx.x & (kLanes - 1)) == 0) reinterpret_cast<float*>(slot + pad)[idx / G] = pk.scale;
+  }
+  static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
+    pk.q = ldg_cg(slot + idx);
+    pk.scale = __uint_as_float(ldg_cg_u32(slot + pad + (idx / G) * 4));
+  }
+};
+
+struct CodecFp8 {
+  static constexpr int kId = CCB_CODEC_FP8;
+  static constexpr int kGroup = 32;
+  struct Packet { uint4 q; uint32_t e; };  // e = biased exponent byte (ue8m0)
+  static __host__ __device__ size_t slot_bytes(size_t pad) { return pad + pad / 32; }
+  // Smallest power of two 2^e with absmax * 2^-e <= 448 (largest e4m3 value).
+  static __device__ __forceinline__ uint32_t scale_byte(float m) {
+    const uint32_t bits = __float_as_uint(m);
+    int e = (int)(bits >> 23) - 127 - 8 + ((bits & 0x7fffffu) > 0x600000u ? 1 : 0);
+    e = max(-126, min(126, e));
+    return (uint32_t)(e + 127);
+  }
+  static __device__ __forceinline__ void encode(const float (&v)[16], Packet& pk) {
+    float m = absmax16(v);
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    pk.e = scale_byte(m);
+    const float inv = __uint_as_float((254u - pk.e) << 23);  // 2^-e
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * k] * inv, v[4 * k + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * k + 2] * inv, v[4 * k + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      w[k] = lo | (hi << 16);
+    }
+    pk.q = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  static __device__ __forceinline__ void decode(const Packet& pk, float (&v)[16]) {
+    const float s = __uint_as_float(pk.e << 23);  // 2^e
+    const uint32_t w[4] = {pk.q.x, pk.q.y, pk.q.z, pk.q.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[k] & 0xffffu), __NV_E4M3);
+      __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[k] >> 16), __NV_E4M3);
+      float2 a = __half22float2(*reinterpret_cast<__half2*>(&lo));
+      float2 b = __half22float2(*reinterpret_cast<__half2*>(&hi));
+      v[4 * k] = a.x * s; v[4 * k + 1] = a.y * s; v[4 * k + 2] = b.x * s; v[4 * k + 3] = b.y * s;
+    }
+  }
+  static __device__ __forceinline__ void store(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    stg(slot + idx, pk.q);
+    if ((threadIdx.x & 1) == 0) reinterpret_cast<uint8_t*>(slot + pad)[idx / 32] = (uint8_t)pk.e;
+  }
+  static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
+    pk.q = ldg_cg(slot + idx);
+    uint32_t e;
+    asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(e) : "l"(slot + pad + idx / 32));
+    pk.e = e & 0xffu;
+  }
+};
+
+}  // namespace ccb

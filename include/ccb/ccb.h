@@ -1,0 +1,89 @@
+/* Public C API of the B200 compressed-collective runtime (libccb.so).
+ *
+ * A communicator owns one symmetric staging arena per rank (CUDA VMM memory whose
+ * handle every peer imports, so a kernel on any GPU can store into any arena over
+ * NVLink) plus flag words for device-side signalling. Every collective below is ONE
+ * kernel launch on the caller's stream: the codec runs in registers and the
+ * compressed bytes are stored directly into the peers' arenas.
+ *
+ * `send`, `recv` and `ef` are arrays with one pointer per LOCAL rank: one entry in
+ * the normal one-process-per-GPU case, `nranks` entries for a communicator made by
+ * ccb_comm_create_local(), which plays all ranks inside a single cooperative launch
+ * on one GPU (used for tests on boxes with fewer GPUs than ranks).
+ *
+ * Calls on one communicator must be issued in the same order on every rank and are
+ * serialised on the GPU in issue order (use one stream per communicator).
+ *
+ * Counterpart in the reference: the LD_PRELOAD wrapper
+ * userconfig/wrapper_code_examples/communication/plain_nccl_compress/
+ * plain_nccl_compress.cu, which builds the same collectives from host-driven
+ * ncclSend/ncclRecv hops around separate quantize / dequantize kernels. */
+#ifndef CCB_H
+#define CCB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "ccb_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ccb_comm ccb_comm;
+typedef void* ccb_stream_t; /* a cudaStream_t */
+
+/* One process per GPU. The CUDA device must be current. `tag` names the rendezvous
+ * (abstract Unix sockets "ccb.<tag>.<rank>"); it must be the same on all ranks and
+ * unique among communicators alive on the host. arena_bytes == 0 picks the default
+ * (CCB_ARENA_MB or 2048 MiB). flags: bit 0 = try to set up an NVLS multicast mapping. */
+int ccb_comm_create(ccb_comm** out, int rank, int nranks, const char* tag, uint64_t arena_bytes, int flags);
+/* All `nranks` ranks on the current device, in one process. */
+int ccb_comm_create_local(ccb_comm** out, int nranks, uint64_t arena_bytes);
+int ccb_comm_destroy(ccb_comm* c);
+int ccb_comm_rank(const ccb_comm* c);   /* first local rank */
+int ccb_comm_nranks(const ccb_comm* c);
+int ccb_comm_nlocal(const ccb_comm* c);
+int ccb_comm_has_nvls(const ccb_comm* c);
+uint64_t ccb_comm_arena_bytes(const ccb_comm* c);
+/* Limit of every device-side wait (default CCB_TIMEOUT_MS or 10000). */
+int ccb_comm_set_timeout_ms(ccb_comm* c, uint64_t ms);
+/* Cap on CTAs per rank (0 = as many as fit). */
+int ccb_comm_set_max_ctas(ccb_comm* c, int ctas);
+/* Copies the CCB_STATUS_WORDS status words; returns CCB_ERR_TIMEOUT when a kernel of
+ * this communicator gave up a wait (the communicator must then be destroyed). Only
+ * meaningful after the stream has been synchronised. */
+int ccb_comm_status(ccb_comm* c, uint32_t* words);
+/* Wire bytes a call moves per rank for `count` elements (for ratio reporting). */
+uint64_t ccb_wire_bytes(int codec, int dtype, uint64_t count);
+
+/* Kernels launched by this library since it was loaded. */
+uint64_t ccb_launch_count(void);
+const char* ccb_last_error(void);
+
+int ccb_all_reduce(ccb_comm* c, const void* const* send, void* const* recv, uint64_t count, int dtype, int op,
+                   int codec, int algo, float* const* ef, ccb_stream_t stream);
+/* recv holds recvcount elements; send holds nranks * recvcount. */
+int ccb_reduce_scatter(ccb_comm* c, const void* const* send, void* const* recv, uint64_t recvcount, int dtype,
+                       int op, int codec, float* const* ef, ccb_stream_t stream);
+int ccb_reduce(ccb_comm* c, const void* const* send, void* const* recv, uint64_t count, int dtype, int op, int root,
+               int codec, ccb_stream_t stream);
+/* General exchange; cnt/send_off/recv_off are nranks x nranks row-major matrices:
+ * cnt[src][dst] elements go from send(src) + send_off[src][dst] to recv(dst) + recv_off[dst][src]. */
+int ccb_exchange(ccb_comm* c, const void* const* send, void* const* recv, const uint64_t* cnt,
+                 const uint64_t* send_off, const uint64_t* recv_off, int dtype, int codec, ccb_stream_t stream);
+int ccb_all_gather(ccb_comm* c, const void* const* send, void* const* recv, uint64_t sendcount, int dtype, int codec,
+                   ccb_stream_t stream);
+int ccb_broadcast(ccb_comm* c, const void* const* send, void* const* recv, uint64_t count, int dtype, int root,
+                  int codec, ccb_stream_t stream);
+int ccb_all_to_all(ccb_comm* c, const void* const* send, void* const* recv, uint64_t count_per_peer, int dtype,
+                   int codec, ccb_stream_t stream);
+int ccb_scatter(ccb_comm* c, const void* const* send, void* const* recv, uint64_t recvcount, int dtype, int root,
+                int codec, ccb_stream_t stream);
+int ccb_gather(ccb_comm* c, const void* const* send, void* const* recv, uint64_t sendcount, int dtype, int root,
+               int codec, ccb_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
