@@ -87,8 +87,22 @@ def main():
     def step():
         comm.all_reduce(x, y, codec=args.codec, algo=args.algo, error_feedback=ef)
 
+    # Warm up for at least W steps AND about a second, so that the clock sampler (one
+    # nvidia-smi sample per 100 ms) sees the GPU under the same load as the timed steps.
+    sampler = ClockSampler(local_rank, 100)
+    sampler.__enter__()
+    t_w = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         step()
+    barrier()
+    per = (time.perf_counter() - t_w) / max(args.warmup, 3)
+    extra = torch.tensor([min(20000, int(1.2 / max(per, 1e-6)) + 1)], device=dev)
+    if world > 1:
+        dist.all_reduce(extra, op=dist.ReduceOp.MAX)  # every rank must issue the same number of calls
+    for i in range(int(extra.item())):
+        step()
+        if i % 16 == 15:
+            torch.cuda.synchronize()
     barrier()
     rc, words = comm.status()
     if rc != 0:
@@ -97,13 +111,14 @@ def main():
     # ---- device-timed region -------------------------------------------------
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     l0 = launch_count()
-    with ClockSampler(local_rank, 100) as clk:
-        barrier()
-        start.record()
-        for _ in range(args.steps):
-            step()
-        stop.record()
-        barrier()
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        step()
+    stop.record()
+    barrier()
+    sampler.__exit__(None, None, None)
+    clk = sampler
     launches = launch_count() - l0
     ms = start.elapsed_time(stop)
     t = torch.tensor([ms], device=dev, dtype=torch.float64)

@@ -105,6 +105,24 @@ class Communicator:
     def set_max_ctas(self, ctas: int) -> None:
         _check(lib().ccb_comm_set_max_ctas(self._h, ctas))
 
+    def set_waves(self, waves: int) -> None:
+        L = lib()
+        L.ccb_comm_set_waves.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        _check(L.ccb_comm_set_waves(self._h, waves))
+
+    def set_trace(self, on: bool) -> None:
+        L = lib()
+        L.ccb_comm_set_trace.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        _check(L.ccb_comm_set_trace(self._h, 1 if on else 0))
+
+    def read_trace(self, ctas: int):
+        """Phase timestamps (ns) of the last traced call as a [ctas, 8] int64 tensor."""
+        L = lib()
+        L.ccb_comm_read_trace.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        out = torch.zeros(ctas, 8, dtype=torch.int64)
+        _check(L.ccb_comm_read_trace(self._h, out.data_ptr(), ctas))
+        return out
+
     def status(self) -> tuple[int, list[int]]:
         words = (ctypes.c_uint32 * 8)()
         rc = lib().ccb_comm_status(self._h, words)

@@ -59,15 +59,22 @@ struct CodecNone {
       }
     }
   }
+  // The wire order inside one 512-element warp unit is register-major: vector k of
+  // lane l sits at ((k * 32 + l) * 16) bytes, so that each store instruction of a warp
+  // writes 512 contiguous bytes (full NVLink packets) instead of 16-byte pieces at a
+  // 16*kQ-byte stride. Only `load` below ever reads this layout back.
+  static __device__ __forceinline__ size_t wire_off(size_t idx, int k) {
+    const size_t unit = idx / kWarpElems;
+    const size_t lane = (idx % kWarpElems) / kLaneElems;
+    return unit * (kWarpElems * sizeof(T)) + ((size_t)k * 32 + lane) * 16;
+  }
   static __device__ __forceinline__ void store(char* slot, size_t pad, size_t idx, const Packet& pk) {
-    char* p = slot + idx * sizeof(T);
 #pragma unroll
-    for (int k = 0; k < kQ; ++k) stg(p + 16 * k, pk.q[k]);
+    for (int k = 0; k < kQ; ++k) stg(slot + wire_off(idx, k), pk.q[k]);
   }
   static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
-    const char* p = slot + idx * sizeof(T);
 #pragma unroll
-    for (int k = 0; k < kQ; ++k) pk.q[k] = ldg_cg(p + 16 * k);
+    for (int k = 0; k < kQ; ++k) pk.q[k] = ldg_cg(slot + wire_off(idx, k));
   }
 };
 

@@ -99,6 +99,13 @@ __device__ __forceinline__ void broadcast_abort(const CommDev& c, uint32_t epoch
   for (int p = 0; p < c.nranks; ++p) st_release_sys(ctrl_ptr(c.arena[p], CCB_CTRL_ABORT), epoch);
 }
 
+// Optional per-CTA phase timestamps (globaltimer, ns) for the perf columns and for
+// tuning: slot k of CTA (blockIdx.y, blockIdx.x). No cost when tracing is off.
+__device__ __forceinline__ void trace_mark(const CommDev& c, int k) {
+  if (c.trace && threadIdx.x == 0)
+    c.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * CCB_TRACE_SLOTS + k] = globaltimer_ns();
+}
+
 // ------------------------------------------------------ element load/store --
 template <class T> struct Elem;
 template <> struct Elem<float> {

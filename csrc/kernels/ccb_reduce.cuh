@@ -60,6 +60,17 @@ __device__ __forceinline__ void end_handshake(CtaSync& s, const CommDev& c, int 
 
 enum { kTwoShot = 0, kOneShot = 1 };
 
+// SHAPE == kOneShot: every rank stores its whole (compressed) message into every
+// arena and reduces all n copies itself: one exchange, n times the bytes; for
+// latency-bound sizes.
+// SHAPE == kTwoShot: shard s is owned by rank s (or the whole message by `root` for
+// Reduce). The CTA's tiles of a shard are cut into `waves` consecutive groups and
+// the three phases are software-pipelined over them,
+//     P1(w+1): compress and store to the owners      (HBM read, NVLink write)
+//     P2(w)  : owner reduces, requantises, stores    (HBM read, NVLink write)
+//     P3(w-1): everybody decodes the reduced shards  (HBM read and write only)
+// so that, across the CTAs of a GPU, link-bound and memory-bound work overlap
+// instead of alternating. Flag row 2w carries phase 1 of wave w, row 2w+1 phase 2.
 template <class T, class C, int SHAPE>
 __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_constant__ ReduceArgs a) {
   __shared__ CtaSync sync;
@@ -76,7 +87,6 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
   const size_t area1 = half, area2 = half + (size_t)n * a.slot_bytes;
   const size_t pad = a.shard_pad;
   const bool rooted = (a.mode == CCB_MODE_REDUCE);
-  const bool oneshot = (SHAPE == kOneShot);
   if (threadIdx.x == 0) sync.fail = 0;
   __syncthreads();
 
@@ -87,7 +97,6 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
     return left < a.shard_elems ? left : a.shard_elems;
   };
 
-  // ---- phase 1: compress what others own and store it into their arenas -----
   if constexpr (SHAPE == kOneShot) {
     const size_t valid = shard_valid(0);
     for (size_t t = b; t * kTileElems < valid; t += G) {
@@ -117,73 +126,92 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
     }
     __syncthreads();
     if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 0, r, b), c.epoch);
-  } else {
-    for (int j = 1; j < n; ++j) {
-      const int p = (r + j) % n;
-      if (rooted && p != a.root) continue;
-      const int s = rooted ? 0 : p;
-      const size_t valid = shard_valid(s);
-      const T* src = send + (size_t)s * a.shard_elems;
-      char* dst = c.arena[p] + area1 + (size_t)r * a.slot_bytes;
-      for (size_t t = b; t * kTileElems < valid; t += G) {
-        if (t * kTileElems + warp_off >= valid) continue;
-        const size_t idx = t * kTileElems + lane_off;
-        float v[16];
-        load16<T>(src, idx, valid, v);
-        float* efs = ef ? ef + (size_t)s * a.shard_elems : nullptr;
-        if (efs) {
-          float e[16];
-          load16f_plain(efs, idx, valid, e);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] += e[i];
-        }
-        typename C::Packet pk;
-        C::encode(v, pk);
-        C::store(dst, pad, idx, pk);
-        if (efs) {
-          float d[16];
-          C::decode(pk, d);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) d[i] = v[i] - d[i];
-          store16f_plain(efs, idx, valid, d);
-        }
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) signal_flag(flag_ptr(c.arena[p], 0, r, b), c.epoch);
-    }
-  }
-
-  // ---- phase 2: the owner reduces its shard in fp32 ---------------------------
-  const bool owner = oneshot || !rooted || r == a.root;
-  if (owner) {
     if (!cta_wait_sources(sync, c, my, 0, r, 0xffu, 0x10)) return;
-    const int s = (oneshot || rooted) ? 0 : r;
-    const size_t valid = shard_valid(s);
-    const T* src = send + (size_t)s * a.shard_elems;
     for (size_t t = b; t * kTileElems < valid; t += G) {
       if (t * kTileElems + warp_off >= valid) continue;
       const size_t idx = t * kTileElems + lane_off;
+      // Every rank sums the same n decoded contributions in the same order, its own
+      // included, so all ranks end with bit-identical results.
       float acc[16];
-      if constexpr (SHAPE == kOneShot) {
-        // Every rank sums the same n decoded contributions in the same order, its own
-        // included, so all ranks end with bit-identical results.
-        bool first = true;
-        for (int q = 0; q < n; ++q) {
+      for (int q = 0; q < n; ++q) {
+        typename C::Packet pk;
+        C::load(my + area1 + (size_t)q * a.slot_bytes, pad, idx, pk);
+        float d[16];
+        C::decode(pk, d);
+        if (q == 0) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = d[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = apply_op(a.op, acc[i], d[i]);
+        }
+      }
+      store16<T>(recv, idx, valid, acc);
+    }
+    return;
+  } else {
+    const int W = a.waves < 1 ? 1 : a.waves;
+    // k-range of this CTA's tiles (t = b + k*G) of a shard that belong to wave w
+    auto wave_range = [&](size_t valid, int w, size_t& kb, size_t& ke) {
+      const size_t nt = (valid + kTileElems - 1) / kTileElems;
+      const size_t K = nt > (size_t)b ? (nt - b + G - 1) / G : 0;
+      kb = K * (size_t)w / W;
+      ke = K * (size_t)(w + 1) / W;
+    };
+
+    auto phase1 = [&](int w) {
+      for (int j = 1; j < n; ++j) {
+        const int p = (r + j) % n;
+        if (rooted && p != a.root) continue;
+        const int s = rooted ? 0 : p;
+        const size_t valid = shard_valid(s);
+        const T* src = send + (size_t)s * a.shard_elems;
+        float* efs = ef ? ef + (size_t)s * a.shard_elems : nullptr;
+        char* dst = c.arena[p] + area1 + (size_t)r * a.slot_bytes;
+        size_t kb, ke;
+        wave_range(valid, w, kb, ke);
+        for (size_t k = kb; k < ke; ++k) {
+          const size_t t = b + k * G;
+          if (t * kTileElems + warp_off >= valid) continue;
+          const size_t idx = t * kTileElems + lane_off;
+          float v[16];
+          load16<T>(src, idx, valid, v);
+          if (efs) {
+            float e[16];
+            load16f_plain(efs, idx, valid, e);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += e[i];
+          }
           typename C::Packet pk;
-          C::load(my + area1 + (size_t)q * a.slot_bytes, pad, idx, pk);
-          float d[16];
-          C::decode(pk, d);
-          if (first) {
+          C::encode(v, pk);
+          C::store(dst, pad, idx, pk);
+          if (efs) {
+            float d[16];
+            C::decode(pk, d);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = d[i];
-            first = false;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = apply_op(a.op, acc[i], d[i]);
+            for (int i = 0; i < 16; ++i) d[i] = v[i] - d[i];
+            store16f_plain(efs, idx, valid, d);
           }
         }
-        store16<T>(recv, idx, valid, acc);
-      } else {
+        __syncthreads();
+        if (threadIdx.x == 0) signal_flag(flag_ptr(c.arena[p], 2 * w, r, b), c.epoch);
+      }
+    };
+
+    auto phase2 = [&](int w) -> bool {
+      if (rooted && r != a.root) return true;
+      if (!cta_wait_sources(sync, c, my, 2 * w, r, 0xffu, 0x10 | (w << 16))) return false;
+      const int s = rooted ? 0 : r;
+      const size_t valid = shard_valid(s);
+      const T* src = send + (size_t)s * a.shard_elems;
+      float* efs = (ef && a.mode == CCB_MODE_ALLREDUCE) ? ef + (size_t)s * a.shard_elems : nullptr;
+      size_t kb, ke;
+      wave_range(valid, w, kb, ke);
+      for (size_t k = kb; k < ke; ++k) {
+        const size_t t = b + k * G;
+        if (t * kTileElems + warp_off >= valid) continue;
+        const size_t idx = t * kTileElems + lane_off;
+        float acc[16];
         load16<T>(src, idx, valid, acc);
         for (int q = 0; q < n; ++q) {
           if (q == r) continue;
@@ -195,7 +223,6 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
           for (int i = 0; i < 16; ++i) acc[i] = apply_op(a.op, acc[i], d[i]);
         }
         if (a.mode == CCB_MODE_ALLREDUCE) {
-          float* efs = ef ? ef + (size_t)s * a.shard_elems : nullptr;
           if (efs) {
             float e[16];
             load16f_plain(efs, idx, valid, e);
@@ -221,29 +248,49 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
           store16<T>(recv, idx, valid, acc);
         }
       }
-    }
-  }
-
-  // ---- phase 3 (two-shot AllReduce): collect the reduced shards ---------------
-  if (SHAPE == kTwoShot && a.mode == CCB_MODE_ALLREDUCE) {
-    __syncthreads();
-    if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 1, r, b), c.epoch);
-    if (!cta_wait_sources(sync, c, my, 1, r, 0xffu, 0x20)) return;
-    for (int j = 1; j < n; ++j) {
-      const int q = (r + j) % n;
-      const size_t valid = shard_valid(q);
-      for (size_t t = b; t * kTileElems < valid; t += G) {
-        if (t * kTileElems + warp_off >= valid) continue;
-        const size_t idx = t * kTileElems + lane_off;
-        typename C::Packet pk;
-        C::load(my + area2 + (size_t)q * a.slot_bytes, pad, idx, pk);
-        float d[16];
-        C::decode(pk, d);
-        store16<T>(recv + (size_t)q * a.shard_elems, idx, valid, d);
+      if (a.mode == CCB_MODE_ALLREDUCE) {
+        __syncthreads();
+        if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 2 * w + 1, r, b), c.epoch);
       }
+      return true;
+    };
+
+    auto phase3 = [&](int w) -> bool {
+      if (!cta_wait_sources(sync, c, my, 2 * w + 1, r, 0xffu, 0x20 | (w << 16))) return false;
+      for (int j = 1; j < n; ++j) {
+        const int q = (r + j) % n;
+        const size_t valid = shard_valid(q);
+        size_t kb, ke;
+        wave_range(valid, w, kb, ke);
+        for (size_t k = kb; k < ke; ++k) {
+          const size_t t = b + k * G;
+          if (t * kTileElems + warp_off >= valid) continue;
+          const size_t idx = t * kTileElems + lane_off;
+          typename C::Packet pk;
+          C::load(my + area2 + (size_t)q * a.slot_bytes, pad, idx, pk);
+          float d[16];
+          C::decode(pk, d);
+          store16<T>(recv + (size_t)q * a.shard_elems, idx, valid, d);
+        }
+      }
+      return true;
+    };
+
+    const bool ar = (a.mode == CCB_MODE_ALLREDUCE);
+    trace_mark(c, 0);
+    phase1(0);
+    trace_mark(c, 1);
+    for (int w = 0; w < W; ++w) {
+      if (w + 1 < W) phase1(w + 1);
+      if (!phase2(w)) return;
+      if (w == 0) trace_mark(c, 2);
+      if (ar && w >= 1 && !phase3(w - 1)) return;
     }
+    trace_mark(c, 3);
+    if (ar && !phase3(W - 1)) return;
+    trace_mark(c, 4);
+    if (rooted) end_handshake(sync, c, r);
   }
-  if (rooted) end_handshake(sync, c, r);
 }
 
 }  // namespace ccb

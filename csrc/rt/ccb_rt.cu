@@ -142,6 +142,8 @@ struct ccb_comm {
   uint32_t epoch = 0;
   int num_sms = 0;
   int max_ctas = 0;
+  int waves = 0;  // 0 = choose per call
+  unsigned long long* trace = nullptr;  // device buffer, CCB_MAX_CTAS * nlocal * CCB_TRACE_SLOTS
   bool dead = false;
   // ownership
   bool vmm = false;
@@ -170,6 +172,7 @@ static int finish_common(ccb_comm* c) {
   c->num_sms = prop.multiProcessorCount;
   c->timeout_ns = env_u64("CCB_TIMEOUT_MS", 10000) * 1000000ull;
   c->max_ctas = (int)env_u64("CCB_MAX_CTAS", 0);
+  c->waves = (int)env_u64("CCB_WAVES", 0);
   RT_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), CCB_STATUS_WORDS * 4, cudaHostAllocMapped));
   memset(c->status_host, 0, CCB_STATUS_WORDS * 4);
   RT_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
@@ -183,6 +186,7 @@ CommDev comm_dev(ccb_comm* c, uint32_t epoch) {
   for (int i = 0; i < c->nranks; ++i) d.arena[i] = c->arena[i];
   d.mc_arena = c->mc_arena;
   d.status = c->status_dev;
+  d.trace = c->trace;
   d.timeout_ns = c->timeout_ns;
   d.half_bytes = c->half_bytes;
   d.epoch = epoch;
@@ -528,6 +532,7 @@ extern "C" int ccb_comm_destroy(ccb_comm* c) {
     if (c->local_alloc[p]) cudaFree(c->local_alloc[p]);
   }
   if (c->status_host) cudaFreeHost(c->status_host);
+  if (c->trace) cudaFree(c->trace);
   (void)cudaGetLastError();
   delete c;
   return CCB_OK;
@@ -546,6 +551,30 @@ extern "C" int ccb_comm_set_timeout_ms(ccb_comm* c, uint64_t ms) {
 extern "C" int ccb_comm_set_max_ctas(ccb_comm* c, int ctas) {
   if (!c) return CCB_ERR_ARG;
   c->max_ctas = ctas;
+  return CCB_OK;
+}
+extern "C" int ccb_comm_set_trace(ccb_comm* c, int on) {
+  if (!c) return CCB_ERR_ARG;
+  const size_t bytes = (size_t)CCB_MAX_CTAS * CCB_MAX_RANKS * CCB_TRACE_SLOTS * sizeof(unsigned long long);
+  if (on && !c->trace) {
+    RT_TRY(cudaMalloc(reinterpret_cast<void**>(&c->trace), bytes));
+    RT_TRY(cudaMemset(c->trace, 0, bytes));
+  } else if (!on && c->trace) {
+    cudaDeviceSynchronize();
+    cudaFree(c->trace);
+    c->trace = nullptr;
+  }
+  return CCB_OK;
+}
+/* Copies the timestamps of the last traced call: out[cta * CCB_TRACE_SLOTS + k]. */
+extern "C" int ccb_comm_read_trace(ccb_comm* c, unsigned long long* out, int ctas) {
+  if (!c || !c->trace || ctas < 1 || ctas > CCB_MAX_CTAS * CCB_MAX_RANKS) return CCB_ERR_ARG;
+  RT_TRY(cudaMemcpy(out, c->trace, (size_t)ctas * CCB_TRACE_SLOTS * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+  return CCB_OK;
+}
+extern "C" int ccb_comm_set_waves(ccb_comm* c, int waves) {
+  if (!c || waves < 0 || waves > CCB_MAX_SLOTS / 2) return CCB_ERR_ARG;
+  c->waves = waves;
   return CCB_OK;
 }
 extern "C" int ccb_comm_status(ccb_comm* c, uint32_t* words) {
@@ -634,7 +663,13 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
   a.op = op;
   a.root = root;
   a.mode = mode;
-  return launch(c, fn, ctas_for(c, fn, shard_elems < count ? shard_elems : count), &a, stream);
+  const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count);
+  // Pipeline depth: each wave should still hold a couple of tiles per CTA.
+  const size_t tiles_per_cta = ((shard_elems < count ? shard_elems : count) / kTileElems) / (size_t)ctas;
+  int waves = c->waves > 0 ? c->waves : (tiles_per_cta >= 8 ? 4 : tiles_per_cta >= 4 ? 2 : 1);
+  if (waves > CCB_MAX_SLOTS / 2) waves = CCB_MAX_SLOTS / 2;
+  a.waves = shape == kTwoShot ? waves : 1;
+  return launch(c, fn, ctas, &a, stream);
 }
 
 int nvls_all_reduce(ccb_comm* c, const void* const* send, void* const* recv, uint64_t count, int dtype, int op,
@@ -964,6 +999,7 @@ extern "C" int ccb_test_partial_all_reduce(ccb_comm* c, const void* send, void* 
   a.rank0 = 0;
   a.nlocal = ranks_played;
   a.mode = CCB_MODE_ALLREDUCE;
+  a.waves = 1;
   dim3 grid(1, (unsigned)ranks_played, 1), block(kThreads, 1, 1);
   void* params[] = {&a};
   cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, block, params, 0, static_cast<cudaStream_t>(stream));

@@ -50,10 +50,17 @@ uint64_t ccb_comm_arena_bytes(const ccb_comm* c);
 int ccb_comm_set_timeout_ms(ccb_comm* c, uint64_t ms);
 /* Cap on CTAs per rank (0 = as many as fit). */
 int ccb_comm_set_max_ctas(ccb_comm* c, int ctas);
+/* Software-pipeline depth of the two-shot kernels (0 = choose per call, at most 8). */
+int ccb_comm_set_waves(ccb_comm* c, int waves);
 /* Copies the CCB_STATUS_WORDS status words; returns CCB_ERR_TIMEOUT when a kernel of
  * this communicator gave up a wait (the communicator must then be destroyed). Only
  * meaningful after the stream has been synchronised. */
 int ccb_comm_status(ccb_comm* c, uint32_t* words);
+/* Device-side phase tracing: when on, every CTA of the two-shot kernels records
+ * globaltimer nanoseconds at its phase boundaries (slots: 0 start, 1 first phase-1
+ * done, 2 first phase-2 done, 3 all phase-2 done, 4 end). */
+int ccb_comm_set_trace(ccb_comm* c, int on);
+int ccb_comm_read_trace(ccb_comm* c, unsigned long long* out, int ctas);
 /* Wire bytes a call moves per rank for `count` elements (for ratio reporting). */
 uint64_t ccb_wire_bytes(int codec, int dtype, uint64_t count);
 

@@ -25,6 +25,8 @@
 #define CCB_STATUS_EPOCH 2
 #define CCB_STATUS_SEEN 3
 #define CCB_STATUS_WORDS 8
+/* Phase trace: CCB_TRACE_SLOTS timestamps per CTA (start, after each phase, end). */
+#define CCB_TRACE_SLOTS 8
 #define CCB_ST_TIMEOUT 1u
 #define CCB_ST_ABORTED 2u
 
@@ -57,6 +59,7 @@ typedef struct CommDev {
   char* arena[CCB_MAX_RANKS]; /* every rank's arena, mapped in this process  */
   char* mc_arena;             /* NVLS multicast mapping of the arenas, or 0  */
   uint32_t* status;           /* CCB_STATUS_WORDS host-mapped words          */
+  unsigned long long* trace;  /* per-CTA phase timestamps (globaltimer ns), or 0 */
   uint64_t timeout_ns;
   uint64_t half_bytes;        /* size of one staging half                    */
   uint32_t epoch;             /* this call's sequence number (never 0)       */
@@ -77,6 +80,7 @@ typedef struct ReduceArgs {
   uint64_t slot_bytes;        /* bytes of one wire slot                       */
   int rank0, nlocal;
   int op, root, mode;
+  int waves;                  /* software-pipeline depth of the two-shot shape  */
 } ReduceArgs;
 enum { CCB_MODE_ALLREDUCE = 0, CCB_MODE_REDUCESCATTER = 1, CCB_MODE_REDUCE = 2 };
 

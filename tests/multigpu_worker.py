@@ -1,0 +1,122 @@
+"""Worker of the multi-GPU tests: one process per GPU under torch.distributed.run.
+Checks every collective over real peer memory against torch.distributed (NCCL) and
+the torch restatements, then prints MULTIGPU_OK on rank 0."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from ccbench_b200 import Communicator  # noqa: E402
+from ccbench_b200.ops import codecs as C  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=dev)
+    want_nvls = os.environ.get("CCB_TEST_NVLS", "1") == "1"
+    comm = Communicator.from_torch_distributed(arena_bytes=512 << 20, nvls=want_nvls)
+    if rank == 0:
+        print("nvls mapping:", comm.has_nvls, flush=True)
+    import traceback
+    try:
+        _body(comm, rank, world, dev)
+    except Exception:
+        print(f"[rank {rank}] FAILED\n" + traceback.format_exc(), flush=True)
+        os._exit(1)
+    dist.barrier()
+    comm.close()
+    if rank == 0:
+        print("MULTIGPU_OK", flush=True)
+    dist.destroy_process_group()
+
+
+def _body(comm, rank, world, dev):
+
+    def gather_inputs(x):
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x)
+        return [t.cpu() for t in xs]
+
+    for dtype in (torch.float32, torch.bfloat16):
+        for count in (1000, 1 << 20, (1 << 22) + 77):
+            g = torch.Generator(device=dev).manual_seed(rank * 1000 + count)
+            x = (torch.randn(count, generator=g, device=dev) * (rank + 1)).to(dtype)
+            xs = gather_inputs(x)
+            exact = sum(t.double() for t in xs).float()
+            for codec in ("int8", "fp8", "none"):
+                for algo in ("twoshot", "oneshot", "ring", "tree"):
+                    y = torch.empty_like(x)
+                    for _ in range(3):
+                        comm.all_reduce(x, y, codec=codec, algo=algo)
+                    torch.cuda.synchronize()
+                    rc, words = comm.status()
+                    assert rc == 0, words
+                    want = C.simulate_all_reduce(xs, codec, algo, dtype)
+                    got = y.float().cpu()
+                    scale = want.abs().max().item()
+                    step = {"int8": 1 / 127, "fp8": 1 / 8, "none": 2 ** -7 if dtype != torch.float32 else 1e-6}[codec]
+                    ulp = 0.0 if dtype == torch.float32 else 2.0 ** -7
+                    d = (got - want).abs()
+                    # a rounding flip at one hop (fp32 summation order, FMA) can be carried and
+                    # widened by the requantisations of the later hops
+                    hops = {"ring": world, "tree": 4, "twoshot": 2, "oneshot": 1}[algo]
+                    assert d.max().item() <= (hops * 1.01 * step + ulp) * scale, (dtype, count, codec, algo, d.max().item())
+                    assert (d > 1e-5 * scale).float().mean().item() < 0.02, (dtype, count, codec, algo)
+                    # all ranks bit-identical
+                    ys = gather_inputs(y)
+                    assert all(torch.equal(ys[0], t) for t in ys), (codec, algo)
+            if comm.has_nvls:
+                y = torch.empty_like(x)
+                for _ in range(3):
+                    comm.all_reduce(x, y, codec="none", algo="nvls")
+                torch.cuda.synchronize()
+                assert comm.status()[0] == 0
+                tol = 1e-5 if dtype == torch.float32 else 2e-2
+                rel = ((y.float().cpu() - exact).norm() / exact.norm()).item()
+                assert rel < tol, ("nvls", dtype, count, rel)
+
+    # reduce_scatter / all_gather / broadcast / all_to_all
+    per = 100003
+    x = torch.randn(per * world, device=dev) * (rank + 1)
+    xs = gather_inputs(x)
+    out = torch.empty(per, device=dev)
+    comm.reduce_scatter(x, out, codec="int8")
+    torch.cuda.synchronize()
+    ex = sum(t[rank * per:(rank + 1) * per].double() for t in xs).float()
+    assert ((out.cpu() - ex).norm() / ex.norm()).item() < 0.03
+    ag = torch.empty(per * world * world, device=dev)
+    comm.all_gather(x, ag, codec="fp8")
+    torch.cuda.synchronize()
+    want = torch.cat([C.roundtrip(t, "fp8") for t in xs])
+    assert torch.equal(ag.cpu(), want)
+    b = torch.empty_like(x)
+    for root in range(world):
+        comm.broadcast(x, b, root=root, codec="int8")
+        torch.cuda.synchronize()
+        wantb = C.roundtrip(xs[root], "int8")
+        if not torch.equal(b.cpu(), wantb):
+            bad = (b.cpu() != wantb).nonzero().flatten()
+            raise AssertionError(f"broadcast root={root} rank={rank}: {bad.numel()} of {wantb.numel()} differ, first at "
+                                 f"{bad[:8].tolist()} got {b.cpu()[bad[:4]].tolist()} want {wantb[bad[:4]].tolist()} "
+                                 f"last {bad[-3:].tolist()}")
+    a2a = torch.empty_like(x)
+    comm.all_to_all(x, a2a, codec="none")
+    torch.cuda.synchronize()
+    want = torch.cat([t[rank * per:(rank + 1) * per] for t in xs])
+    assert torch.equal(a2a.cpu(), want)
+    red = torch.zeros_like(x)
+    for _ in range(3):
+        comm.reduce(x, red, root=world - 1, codec="none")
+    torch.cuda.synchronize()
+    if rank == world - 1:
+        ex = sum(t.double() for t in xs).float()
+        assert torch.allclose(red.cpu(), ex, rtol=1e-5, atol=1e-5)
+    assert comm.status()[0] == 0
+
+
+if __name__ == "__main__":
+    main()

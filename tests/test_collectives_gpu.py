@@ -33,14 +33,15 @@ def _inputs(n, count, dtype, seed=0):
     return xs, [x.cuda() for x in xs]
 
 
-def _close(got, want, exact_ref, codec, dtype):
+def _close(got, want, exact_ref, codec, dtype, hops=2):
     """got vs the simulated algorithm: equal up to fp32 summation-order noise, which can
     flip the rounding of an occasional code; and bounded against the exact sum."""
     got = got.float().cpu()
     diff = (got - want).abs()
     scale = want.abs().max().item() + 1e-30
     step = {"int8": 1 / 127, "int8_g256": 1 / 127, "fp8": 1 / 8, "none": 2 ** -7 if dtype != torch.float32 else 1e-6}[codec]
-    assert diff.max().item() <= 1.01 * step * scale, f"max diff {diff.max().item()} vs step {step * scale}"
+    ulp = 0.0 if dtype == torch.float32 else 2.0 ** -7  # one rounding flip of the 16-bit output
+    assert diff.max().item() <= (hops * 1.01 * step + ulp) * scale, f"max diff {diff.max().item()} vs step {step * scale}"
     frac = (diff > 1e-5 * scale).float().mean().item()
     assert frac < 0.02, f"{frac:.4f} of elements differ from the restated algorithm"
     rel = ((got - exact_ref).norm() / (exact_ref.norm() + 1e-30)).item()
@@ -62,8 +63,9 @@ def test_all_reduce(comms, algo, codec, dt, n, count):
     assert comm.status()[0] == 0
     want = C.simulate_all_reduce(xs, codec, algo, dtype)
     exact = sum(x.double() for x in xs).float()
+    hops = {"ring": max(n, 2), "tree": 4, "twoshot": 2, "oneshot": 2}[algo]
     for r in range(n):
-        _close(out[r], want, exact, codec, dtype)
+        _close(out[r], want, exact, codec, dtype, hops)
         assert torch.equal(out[r], out[0]), "ranks must hold bit-identical results"
 
 
