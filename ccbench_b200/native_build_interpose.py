@@ -1,0 +1,25 @@
+"""Builds the interposers and wrapper helper libraries into bin/libs."""
+from __future__ import annotations
+
+from . import native_build as nb
+from ._lib import LIBCCB, build_native
+
+
+def build(verbose: bool = False) -> None:
+    root, libs = nb.ROOT, nb.BIN / "libs"
+    build_native(verbose=verbose)
+    # libccb.so is copied next to the interposer so that $ORIGIN finds it
+    dst = libs / "libccb.so"
+    if nb._newer(dst, [LIBCCB]):
+        libs.mkdir(parents=True, exist_ok=True)
+        dst.write_bytes(LIBCCB.read_bytes())
+        dst.chmod(0o755)
+    rpath = ["-Wl,-rpath,$ORIGIN"]
+    nb.cc(libs / "libccb_nccl.so", [root / "csrc/interpose/ccb_nccl_interpose.c"], shared=True,
+          libs=[str(dst), *nb.cuda_libs(), "-ldl", "-lpthread", *rpath], verbose=verbose)
+    for name, src, extra in [
+        ("libnccl_compress_tools.so", root / "csrc/wrappers/nccl_compress_tools.c", [*nb.cuda_libs(), "-lnccl"]),
+        ("libccb_coccl_hooks.so", root / "csrc/wrappers/coccl_hooks.c", [str(dst), *nb.cuda_libs(), *rpath]),
+    ]:
+        if src.exists():
+            nb.cc(libs / name, [src], shared=True, libs=extra, verbose=verbose)

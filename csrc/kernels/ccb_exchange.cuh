@@ -21,6 +21,10 @@ __global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const __grid_cons
   const int b = blockIdx.x, G = gridDim.x;
   const int lane_off = (threadIdx.x >> 5) * kWarpElems + (threadIdx.x & 31) * kLaneElems;
   const int warp_off = (threadIdx.x >> 5) * kWarpElems;
+  // A tile is tile_warps x 512 elements: mid-size messages use narrow tiles so that they
+  // still spread over all CTAs; warps beyond tile_warps only take part in the barriers.
+  const size_t tile_elems = (size_t)a.tile_warps * kWarpElems;
+  const bool active_warp = (int)(threadIdx.x >> 5) < a.tile_warps;
   const T* send = static_cast<const T*>(a.send[lr]);
   T* recv = static_cast<T*>(a.recv[lr]);
   char* my = c.arena[r];
@@ -43,9 +47,9 @@ __global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const __grid_cons
     const int f = __ffs(dstmask) - 1;
     const size_t valid = a.cnt[r][f];
     const T* src = send + a.send_off[r][f];
-    for (size_t t = b; t * kTileElems < valid; t += G) {
-      if (t * kTileElems + warp_off >= valid) continue;
-      const size_t idx = t * kTileElems + lane_off;
+    for (size_t t = b; t * tile_elems < valid; t += G) {
+      if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+      const size_t idx = t * tile_elems + lane_off;
       float v[16];
       load16<T>(src, idx, valid, v);
       typename C::Packet pk;
@@ -62,9 +66,9 @@ __global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const __grid_cons
       if (valid == 0) continue;
       const T* src = send + a.send_off[r][p];
       char* dst = c.arena[p] + area + (size_t)r * a.slot_bytes;
-      for (size_t t = b; t * kTileElems < valid; t += G) {
-        if (t * kTileElems + warp_off >= valid) continue;
-        const size_t idx = t * kTileElems + lane_off;
+      for (size_t t = b; t * tile_elems < valid; t += G) {
+        if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+        const size_t idx = t * tile_elems + lane_off;
         float v[16];
         load16<T>(src, idx, valid, v);
         typename C::Packet pk;
@@ -86,9 +90,9 @@ __global__ void __launch_bounds__(kThreads, 2) exchange_kernel(const __grid_cons
     const size_t valid = a.cnt[q][r];
     if (valid == 0) continue;
     T* dst = recv + a.recv_off[r][q];
-    for (size_t t = b; t * kTileElems < valid; t += G) {
-      if (t * kTileElems + warp_off >= valid) continue;
-      const size_t idx = t * kTileElems + lane_off;
+    for (size_t t = b; t * tile_elems < valid; t += G) {
+      if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+      const size_t idx = t * tile_elems + lane_off;
       typename C::Packet pk;
       C::load(my + area + (size_t)q * a.slot_bytes, pad, idx, pk);
       float d[16];

@@ -79,6 +79,10 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
   const int b = blockIdx.x, G = gridDim.x;
   const int lane_off = (threadIdx.x >> 5) * kWarpElems + (threadIdx.x & 31) * kLaneElems;
   const int warp_off = (threadIdx.x >> 5) * kWarpElems;
+  // A tile is tile_warps x 512 elements: mid-size messages use narrow tiles so that they
+  // still spread over all CTAs; warps beyond tile_warps only take part in the barriers.
+  const size_t tile_elems = (size_t)a.tile_warps * kWarpElems;
+  const bool active_warp = (int)(threadIdx.x >> 5) < a.tile_warps;
   const T* send = static_cast<const T*>(a.send[lr]);
   T* recv = static_cast<T*>(a.recv[lr]);
   float* ef = a.ef[lr];
@@ -99,9 +103,9 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
 
   if constexpr (SHAPE == kOneShot) {
     const size_t valid = shard_valid(0);
-    for (size_t t = b; t * kTileElems < valid; t += G) {
-      if (t * kTileElems + warp_off >= valid) continue;
-      const size_t idx = t * kTileElems + lane_off;
+    for (size_t t = b; t * tile_elems < valid; t += G) {
+      if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+      const size_t idx = t * tile_elems + lane_off;
       float v[16];
       load16<T>(send, idx, valid, v);
       if (ef) {
@@ -127,9 +131,9 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
     __syncthreads();
     if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 0, r, b), c.epoch);
     if (!cta_wait_sources(sync, c, my, 0, r, 0xffu, 0x10)) return;
-    for (size_t t = b; t * kTileElems < valid; t += G) {
-      if (t * kTileElems + warp_off >= valid) continue;
-      const size_t idx = t * kTileElems + lane_off;
+    for (size_t t = b; t * tile_elems < valid; t += G) {
+      if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+      const size_t idx = t * tile_elems + lane_off;
       // Every rank sums the same n decoded contributions in the same order, its own
       // included, so all ranks end with bit-identical results.
       float acc[16];
@@ -153,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
     const int W = a.waves < 1 ? 1 : a.waves;
     // k-range of this CTA's tiles (t = b + k*G) of a shard that belong to wave w
     auto wave_range = [&](size_t valid, int w, size_t& kb, size_t& ke) {
-      const size_t nt = (valid + kTileElems - 1) / kTileElems;
+      const size_t nt = (valid + tile_elems - 1) / tile_elems;
       const size_t K = nt > (size_t)b ? (nt - b + G - 1) / G : 0;
       kb = K * (size_t)w / W;
       ke = K * (size_t)(w + 1) / W;
@@ -172,8 +176,8 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
         wave_range(valid, w, kb, ke);
         for (size_t k = kb; k < ke; ++k) {
           const size_t t = b + k * G;
-          if (t * kTileElems + warp_off >= valid) continue;
-          const size_t idx = t * kTileElems + lane_off;
+          if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+          const size_t idx = t * tile_elems + lane_off;
           float v[16];
           load16<T>(src, idx, valid, v);
           if (efs) {
@@ -209,8 +213,8 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
       wave_range(valid, w, kb, ke);
       for (size_t k = kb; k < ke; ++k) {
         const size_t t = b + k * G;
-        if (t * kTileElems + warp_off >= valid) continue;
-        const size_t idx = t * kTileElems + lane_off;
+        if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+        const size_t idx = t * tile_elems + lane_off;
         float acc[16];
         load16<T>(src, idx, valid, acc);
         for (int q = 0; q < n; ++q) {
@@ -264,8 +268,8 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
         wave_range(valid, w, kb, ke);
         for (size_t k = kb; k < ke; ++k) {
           const size_t t = b + k * G;
-          if (t * kTileElems + warp_off >= valid) continue;
-          const size_t idx = t * kTileElems + lane_off;
+          if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+          const size_t idx = t * tile_elems + lane_off;
           typename C::Packet pk;
           C::load(my + area2 + (size_t)q * a.slot_bytes, pad, idx, pk);
           float d[16];

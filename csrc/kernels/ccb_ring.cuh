@@ -40,6 +40,10 @@ __global__ void __launch_bounds__(kThreads, 2) ring_kernel(const __grid_constant
   const int b = blockIdx.x, G = gridDim.x;
   const int lane_off = (threadIdx.x >> 5) * kWarpElems + (threadIdx.x & 31) * kLaneElems;
   const int warp_off = (threadIdx.x >> 5) * kWarpElems;
+  // A tile is tile_warps x 512 elements: mid-size messages use narrow tiles so that they
+  // still spread over all CTAs; warps beyond tile_warps only take part in the barriers.
+  const size_t tile_elems = (size_t)a.tile_warps * kWarpElems;
+  const bool active_warp = (int)(threadIdx.x >> 5) < a.tile_warps;
   const T* send = static_cast<const T*>(a.send[lr]);
   T* recv = static_cast<T*>(a.recv[lr]);
   float* ef = a.ef[lr];
@@ -68,9 +72,9 @@ __global__ void __launch_bounds__(kThreads, 2) ring_kernel(const __grid_constant
     const size_t valid = shard_valid(cs);
     const T* src = send + (size_t)cs * a.shard_elems;
     float* efs = ef ? ef + (size_t)cs * a.shard_elems : nullptr;
-    for (size_t t = b; t * kTileElems < valid; t += G) {
-      if (t * kTileElems + warp_off >= valid) continue;
-      const size_t idx = t * kTileElems + lane_off;
+    for (size_t t = b; t * tile_elems < valid; t += G) {
+      if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+      const size_t idx = t * tile_elems + lane_off;
       float v[16];
       load16<T>(src, idx, valid, v);
       if (s > 0) {
@@ -117,9 +121,9 @@ __global__ void __launch_bounds__(kThreads, 2) ring_kernel(const __grid_constant
     const int cg = ((r + 1 - k) % n + n) % n;  // chunk that arrives at all-gather hop k
     const bool forward = (k < n - 1);
     const size_t valid = shard_valid(cg);
-    for (size_t t = b; t * kTileElems < valid; t += G) {
-      if (t * kTileElems + warp_off >= valid) continue;
-      const size_t idx = t * kTileElems + lane_off;
+    for (size_t t = b; t * tile_elems < valid; t += G) {
+      if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+      const size_t idx = t * tile_elems + lane_off;
       typename C::Packet pk;
       C::load(my + slot(in_slot), pad, idx, pk);
       if (forward) C::store(nx + slot(in_slot + 1), pad, idx, pk);
@@ -142,6 +146,10 @@ __global__ void __launch_bounds__(kThreads, 2) tree_kernel(const __grid_constant
   const int b = blockIdx.x, G = gridDim.x;
   const int lane_off = (threadIdx.x >> 5) * kWarpElems + (threadIdx.x & 31) * kLaneElems;
   const int warp_off = (threadIdx.x >> 5) * kWarpElems;
+  // A tile is tile_warps x 512 elements: mid-size messages use narrow tiles so that they
+  // still spread over all CTAs; warps beyond tile_warps only take part in the barriers.
+  const size_t tile_elems = (size_t)a.tile_warps * kWarpElems;
+  const bool active_warp = (int)(threadIdx.x >> 5) < a.tile_warps;
   const T* send = static_cast<const T*>(a.send[lr]);
   T* recv = static_cast<T*>(a.recv[lr]);
   float* ef = a.ef[lr];
@@ -170,9 +178,9 @@ __global__ void __launch_bounds__(kThreads, 2) tree_kernel(const __grid_constant
     return;
   }
   char* parent = r == 0 ? nullptr : c.arena[r - (1 << tz)];
-  for (size_t t = b; t * kTileElems < valid; t += G) {
-    if (t * kTileElems + warp_off >= valid) continue;
-    const size_t idx = t * kTileElems + lane_off;
+  for (size_t t = b; t * tile_elems < valid; t += G) {
+    if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+    const size_t idx = t * tile_elems + lane_off;
     float v[16];
     load16<T>(send, idx, valid, v);
     for (int k = 0; k < tz; ++k) {
@@ -222,9 +230,9 @@ __global__ void __launch_bounds__(kThreads, 2) tree_kernel(const __grid_constant
 
   // ---- down: take the encoded total from the parent, pass it on verbatim -------
   if (!cta_wait_slot(sync, c, my, L, 0x70)) return;
-  for (size_t t = b; t * kTileElems < valid; t += G) {
-    if (t * kTileElems + warp_off >= valid) continue;
-    const size_t idx = t * kTileElems + lane_off;
+  for (size_t t = b; t * tile_elems < valid; t += G) {
+    if (!active_warp || t * tile_elems + warp_off >= valid) continue;
+    const size_t idx = t * tile_elems + lane_off;
     typename C::Packet pk;
     C::load(my + slot(L), pad, idx, pk);
     for (int k = 0; k < tz; ++k)

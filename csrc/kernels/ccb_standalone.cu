@@ -1,0 +1,248 @@
+// Stand-alone codec kernels on local memory: encode, decode, decode+add,
+// decode+add+re-encode of several inputs. They back the COCCL-style hook ABI
+// (ncclCompress / ncclDecompress / ncclDecompressReduce / ncclDecompReduceComp), the
+// nccl_send_compressed / nccl_recv_decompress helpers and the point-to-point path of
+// the interposer, and decode the reference wrapper's own int8 wire
+// ([f32 127/absmax x groups][int8 x count], plain_nccl_compress.cu:123-129).
+//
+// Reference kernels replaced: quantize_{f32,f16,f64}_i8, dequantize_i8_* and
+// reduce_* (plain_nccl_compress.cu:141-325: one element per thread, a shared-memory
+// tree reduction per group, grids capped at 65535 blocks without a grid-stride loop)
+// and add_*_kernel (coccl_wrapper_template.cu:258-272). Here a lane owns 16 elements,
+// the group maximum is a few warp shuffles, and every kernel is grid-stride.
+#include <cuda_runtime.h>
+
+#include "../rt/ccb_rt_internal.h"
+#include "ccb_codec.cuh"
+
+namespace ccb {
+
+constexpr int kSaThreads = 256;
+
+template <class T, class C>
+__global__ void __launch_bounds__(kSaThreads) encode_kernel(const T* __restrict__ in, size_t count, char* wire, size_t pad) {
+  const size_t units = pad / kWarpElems;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (size_t u = warp; u < units; u += nwarps) {
+    const size_t idx = u * kWarpElems + (size_t)lane * kLaneElems;
+    float v[16];
+    load16<T>(in, idx, count, v);
+    typename C::Packet pk;
+    C::encode(v, pk);
+    C::store(wire, pad, idx, pk);
+  }
+}
+
+// MODE 0: out = decode(wire); MODE 1: out += decode(wire)
+template <class T, class C, int MODE>
+__global__ void __launch_bounds__(kSaThreads) decode_kernel(const char* wire, size_t count, T* out, size_t pad) {
+  const size_t units = pad / kWarpElems;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (size_t u = warp; u < units; u += nwarps) {
+    const size_t idx = u * kWarpElems + (size_t)lane * kLaneElems;
+    if (idx >= count) continue;
+    typename C::Packet pk;
+    C::load(wire, pad, idx, pk);
+    float d[16];
+    C::decode(pk, d);
+    if (MODE == 1) {
+      float a[16];
+      load16<T>(out, idx, count, a);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) d[i] += a[i];
+    }
+    store16<T>(out, idx, count, d);
+  }
+}
+
+struct WireList {
+  const char* w[16];
+  int n;
+};
+
+// wire_out = encode(sum_k decode(wires[k]))
+template <class C>
+__global__ void __launch_bounds__(kSaThreads) reduce_recode_kernel(const __grid_constant__ WireList wl, size_t count, char* wire_out, size_t pad) {
+  const size_t units = pad / kWarpElems;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (size_t u = warp; u < units; u += nwarps) {
+    const size_t idx = u * kWarpElems + (size_t)lane * kLaneElems;
+    float acc[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+    for (int k = 0; k < wl.n; ++k) {
+      typename C::Packet pk;
+      C::load(wl.w[k], pad, idx, pk);
+      float d[16];
+      C::decode(pk, d);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] += d[i];
+    }
+    typename C::Packet out;
+    C::encode(acc, out);
+    C::store(wire_out, pad, idx, out);
+  }
+}
+
+// Reference wire v0: scales[g] = 127/absmax (1.0 when absmax < 1e-10), then int8 payload.
+template <class T>
+__global__ void __launch_bounds__(kSaThreads) refwire_encode_kernel(const T* __restrict__ in, size_t count, int group, float* scales, int8_t* q) {
+  // one warp per group; group <= 4096
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const size_t ngroups = (count + group - 1) / group;
+  for (size_t g = warp; g < ngroups; g += nwarps) {
+    const size_t lo = g * group, hi = lo + group < count ? lo + group : count;
+    float m = 0.f;
+    for (size_t i = lo + lane; i < hi; i += 32) m = fmaxf(m, fabsf(Elem<T>::to_f(in[i])));
+#pragma unroll
+    for (int d = 16; d; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    const float inv = m < 1e-10f ? 1.0f : 127.0f / m;
+    if (lane == 0) scales[g] = inv;
+    for (size_t i = lo + lane; i < hi; i += 32) {
+      float r = rintf(Elem<T>::to_f(in[i]) * inv);
+      q[i] = (int8_t)fminf(fmaxf(r, -128.f), 127.f);
+    }
+  }
+}
+template <class T>
+__global__ void __launch_bounds__(kSaThreads) refwire_decode_kernel(const float* scales, const int8_t* q, size_t count, int group, T* out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = Elem<T>::from_f((float)q[i] * (1.0f / scales[i / group]));
+}
+
+static int sa_grid(size_t units) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  size_t blocks = (units + (kSaThreads / 32) - 1) / (kSaThreads / 32);
+  size_t cap = (size_t)sms * 8;
+  if (blocks < 1) blocks = 1;
+  return (int)(blocks < cap ? blocks : cap);
+}
+
+template <class T>
+static int encode_t(int codec, const void* in, size_t count, void* wire, size_t pad, cudaStream_t s) {
+  const int g = sa_grid(pad / kWarpElems);
+  switch (codec) {
+    case CCB_CODEC_NONE: encode_kernel<T, CodecNone<T>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
+    case CCB_CODEC_INT8: encode_kernel<T, CodecInt8<128>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
+    case CCB_CODEC_INT8_G256: encode_kernel<T, CodecInt8<256>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
+    case CCB_CODEC_FP8: encode_kernel<T, CodecFp8><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
+    default: return CCB_ERR_UNSUPPORTED;
+  }
+  return CCB_OK;
+}
+template <class T, int MODE>
+static int decode_t(int codec, const void* wire, size_t count, void* out, size_t pad, cudaStream_t s) {
+  const int g = sa_grid(pad / kWarpElems);
+  switch (codec) {
+    case CCB_CODEC_NONE: decode_kernel<T, CodecNone<T>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
+    case CCB_CODEC_INT8: decode_kernel<T, CodecInt8<128>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
+    case CCB_CODEC_INT8_G256: decode_kernel<T, CodecInt8<256>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
+    case CCB_CODEC_FP8: decode_kernel<T, CodecFp8, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
+    default: return CCB_ERR_UNSUPPORTED;
+  }
+  return CCB_OK;
+}
+
+static int finish(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: %s", what, cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  count_launch();
+  return CCB_OK;
+}
+
+}  // namespace ccb
+
+using namespace ccb;
+
+static size_t pad_of(uint64_t count) { return (count + kWarpElems - 1) / kWarpElems * kWarpElems; }
+
+extern "C" int ccb_encode(int codec, int dtype, const void* in, uint64_t count, void* wire, void* stream) {
+  if (!count) return CCB_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = dtype == CCB_F32    ? encode_t<float>(codec, in, count, wire, pad_of(count), s)
+           : dtype == CCB_BF16 ? encode_t<__nv_bfloat16>(codec, in, count, wire, pad_of(count), s)
+           : dtype == CCB_F16  ? encode_t<__half>(codec, in, count, wire, pad_of(count), s)
+                               : CCB_ERR_UNSUPPORTED;
+  return rc ? rc : finish("ccb_encode");
+}
+
+extern "C" int ccb_decode(int codec, int dtype, const void* wire, uint64_t count, void* out, void* stream) {
+  if (!count) return CCB_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = dtype == CCB_F32    ? decode_t<float, 0>(codec, wire, count, out, pad_of(count), s)
+           : dtype == CCB_BF16 ? decode_t<__nv_bfloat16, 0>(codec, wire, count, out, pad_of(count), s)
+           : dtype == CCB_F16  ? decode_t<__half, 0>(codec, wire, count, out, pad_of(count), s)
+                               : CCB_ERR_UNSUPPORTED;
+  return rc ? rc : finish("ccb_decode");
+}
+
+extern "C" int ccb_decode_reduce(int codec, int dtype, const void* wire, uint64_t count, void* inout, void* stream) {
+  if (!count) return CCB_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = dtype == CCB_F32    ? decode_t<float, 1>(codec, wire, count, inout, pad_of(count), s)
+           : dtype == CCB_BF16 ? decode_t<__nv_bfloat16, 1>(codec, wire, count, inout, pad_of(count), s)
+           : dtype == CCB_F16  ? decode_t<__half, 1>(codec, wire, count, inout, pad_of(count), s)
+                               : CCB_ERR_UNSUPPORTED;
+  return rc ? rc : finish("ccb_decode_reduce");
+}
+
+extern "C" int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out, void* stream) {
+  if (!count) return CCB_OK;
+  if (nwires < 1 || nwires > 16) {
+    set_error("ccb_reduce_recode takes 1..16 inputs");
+    return CCB_ERR_ARG;
+  }
+  WireList wl;
+  wl.n = nwires;
+  for (int i = 0; i < nwires; ++i) wl.w[i] = static_cast<const char*>(wires[i]);
+  const size_t pad = pad_of(count);
+  const int g = sa_grid(pad / kWarpElems);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (codec) {
+    case CCB_CODEC_INT8: reduce_recode_kernel<CodecInt8<128>><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
+    case CCB_CODEC_INT8_G256: reduce_recode_kernel<CodecInt8<256>><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
+    case CCB_CODEC_FP8: reduce_recode_kernel<CodecFp8><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
+    case CCB_CODEC_NONE: reduce_recode_kernel<CodecNone<float>><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
+    default: return CCB_ERR_UNSUPPORTED;
+  }
+  return finish("ccb_reduce_recode");
+}
+
+// Reference wire v0 (see the file comment). `wire` holds ceil(count/group) floats then count int8.
+extern "C" int ccb_refwire_encode(int dtype, const void* in, uint64_t count, int group, void* wire, void* stream) {
+  if (!count) return CCB_OK;
+  if (group < 1 || group > 4096) return CCB_ERR_ARG;
+  const size_t ng = (count + group - 1) / group;
+  float* scales = static_cast<float*>(wire);
+  int8_t* q = reinterpret_cast<int8_t*>(scales + ng);
+  const int g = sa_grid(ng);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == CCB_F32) refwire_encode_kernel<float><<<g, kSaThreads, 0, s>>>((const float*)in, count, group, scales, q);
+  else if (dtype == CCB_F16) refwire_encode_kernel<__half><<<g, kSaThreads, 0, s>>>((const __half*)in, count, group, scales, q);
+  else if (dtype == CCB_BF16) refwire_encode_kernel<__nv_bfloat16><<<g, kSaThreads, 0, s>>>((const __nv_bfloat16*)in, count, group, scales, q);
+  else return CCB_ERR_UNSUPPORTED;
+  return finish("ccb_refwire_encode");
+}
+extern "C" int ccb_refwire_decode(int dtype, const void* wire, uint64_t count, int group, void* out, void* stream) {
+  if (!count) return CCB_OK;
+  if (group < 1 || group > 4096) return CCB_ERR_ARG;
+  const size_t ng = (count + group - 1) / group;
+  const float* scales = static_cast<const float*>(wire);
+  const int8_t* q = reinterpret_cast<const int8_t*>(scales + ng);
+  const int g = sa_grid((count + 255) / 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == CCB_F32) refwire_decode_kernel<float><<<g, kSaThreads, 0, s>>>(scales, q, count, group, (float*)out);
+  else if (dtype == CCB_F16) refwire_decode_kernel<__half><<<g, kSaThreads, 0, s>>>(scales, q, count, group, (__half*)out);
+  else if (dtype == CCB_BF16) refwire_decode_kernel<__nv_bfloat16><<<g, kSaThreads, 0, s>>>(scales, q, count, group, (__nv_bfloat16*)out);
+  else return CCB_ERR_UNSUPPORTED;
+  return finish("ccb_refwire_decode");
+}

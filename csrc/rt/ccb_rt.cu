@@ -628,9 +628,16 @@ static const void* tree_fn(int dtype, int codec) {
   return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&tree_kernel<TT, CC>)));
 }
 
-static int ctas_for(ccb_comm* c, const void* fn, size_t elems) {
-  size_t tiles = (elems + kTileElems - 1) / kTileElems;
-  int cap = grid_cap(c, fn);
+// Picks the tile width (in warps, a power of two up to 16) and the number of CTAs per
+// rank for `elems` elements per shard: the widest tile that still gives every
+// resident CTA work, so that mid-size messages are not served by a handful of CTAs.
+static int ctas_for(ccb_comm* c, const void* fn, size_t elems, int* tile_warps) {
+  const int cap = grid_cap(c, fn);
+  const size_t units = (elems + kWarpElems - 1) / kWarpElems;
+  int tw = kWarps;
+  while (tw > 1 && units / (size_t)tw < (size_t)cap) tw >>= 1;
+  *tile_warps = tw;
+  size_t tiles = (units + tw - 1) / tw;
   if (tiles < 1) tiles = 1;
   return tiles < (size_t)cap ? (int)tiles : cap;
 }
@@ -663,9 +670,9 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
   a.op = op;
   a.root = root;
   a.mode = mode;
-  const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count);
+  const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count, &a.tile_warps);
   // Pipeline depth: each wave should still hold a couple of tiles per CTA.
-  const size_t tiles_per_cta = ((shard_elems < count ? shard_elems : count) / kTileElems) / (size_t)ctas;
+  const size_t tiles_per_cta = ((shard_elems < count ? shard_elems : count) / ((size_t)a.tile_warps * kWarpElems)) / (size_t)ctas;
   int waves = c->waves > 0 ? c->waves : (tiles_per_cta >= 8 ? 4 : tiles_per_cta >= 4 ? 2 : 1);
   if (waves > CCB_MAX_SLOTS / 2) waves = CCB_MAX_SLOTS / 2;
   a.waves = shape == kTwoShot ? waves : 1;
@@ -791,7 +798,8 @@ extern "C" int ccb_all_reduce(ccb_comm* c, const void* const* send, void* const*
       a.nlocal = c->nlocal;
       a.op = op;
       a.mode = CCB_MODE_ALLREDUCE;
-      rc = launch(c, fn, ctas_for(c, fn, a.shard_elems < slice ? a.shard_elems : slice), &a, stream);
+      const int ctas = ctas_for(c, fn, a.shard_elems < slice ? a.shard_elems : slice, &a.tile_warps);
+      rc = launch(c, fn, ctas, &a, stream);
       if (rc) return rc;
       done += slice;
     }
@@ -902,7 +910,8 @@ extern "C" int ccb_exchange(ccb_comm* c, const void* const* send, void* const* r
   a.rank0 = c->rank0;
   a.nlocal = c->nlocal;
   a.ack = full ? 0 : 1;
-  return launch(c, fn, ctas_for(c, fn, maxcnt), &a, static_cast<cudaStream_t>(stream_));
+  const int ctas = ctas_for(c, fn, maxcnt, &a.tile_warps);
+  return launch(c, fn, ctas, &a, static_cast<cudaStream_t>(stream_));
 }
 
 namespace {
@@ -1000,6 +1009,7 @@ extern "C" int ccb_test_partial_all_reduce(ccb_comm* c, const void* send, void* 
   a.nlocal = ranks_played;
   a.mode = CCB_MODE_ALLREDUCE;
   a.waves = 1;
+  a.tile_warps = kWarps;
   dim3 grid(1, (unsigned)ranks_played, 1), block(kThreads, 1, 1);
   void* params[] = {&a};
   cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, block, params, 0, static_cast<cudaStream_t>(stream));

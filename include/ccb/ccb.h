@@ -90,6 +90,20 @@ int ccb_scatter(ccb_comm* c, const void* const* send, void* const* recv, uint64_
 int ccb_gather(ccb_comm* c, const void* const* send, void* const* recv, uint64_t sendcount, int dtype, int root,
                int codec, ccb_stream_t stream);
 
+/* ---- stand-alone codec kernels on local memory --------------------------------
+ * Wire layout of `count` elements: pad = count rounded up to 512,
+ * [payload: pad elements][scales: pad / group entries], ccb_wire_bytes() bytes. */
+int ccb_encode(int codec, int dtype, const void* in, uint64_t count, void* wire, ccb_stream_t stream);
+int ccb_decode(int codec, int dtype, const void* wire, uint64_t count, void* out, ccb_stream_t stream);
+/* inout += decode(wire) */
+int ccb_decode_reduce(int codec, int dtype, const void* wire, uint64_t count, void* inout, ccb_stream_t stream);
+/* wire_out = encode(sum_k decode(wires[k])), 1 <= nwires <= 16 */
+int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out,
+                      ccb_stream_t stream);
+/* The reference wrapper's int8 wire: [f32 127/absmax per group][int8 x count]. */
+int ccb_refwire_encode(int dtype, const void* in, uint64_t count, int group, void* wire, ccb_stream_t stream);
+int ccb_refwire_decode(int dtype, const void* wire, uint64_t count, int group, void* out, ccb_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,6 +81,7 @@ typedef struct ReduceArgs {
   int rank0, nlocal;
   int op, root, mode;
   int waves;                  /* software-pipeline depth of the two-shot shape  */
+  int tile_warps;             /* warps of a CTA that carry data: tile = 512 * tile_warps */
 } ReduceArgs;
 enum { CCB_MODE_ALLREDUCE = 0, CCB_MODE_REDUCESCATTER = 1, CCB_MODE_REDUCE = 2 };
 
@@ -98,6 +99,7 @@ typedef struct ExchangeArgs {
   uint64_t slot_bytes;
   int rank0, nlocal;
   int ack;             /* rooted pattern: finish with an all-rank handshake     */
+  int tile_warps;
 } ExchangeArgs;
 
 #endif
