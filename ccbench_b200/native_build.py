@@ -18,7 +18,7 @@ BIN = ROOT / "bin"
 CUDA = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 INC = [ROOT / "include" / "ccb" / "compat", ROOT / "include", ROOT / "userconfig" / "deviation_metric_examples",
        CUDA / "include"]
-CFLAGS = ["-O2", "-g", "-Wall", "-Wno-unused-function", "-fPIC"]
+CFLAGS = ["-O2", "-g", "-Wall", "-Wno-unused-function", "-Wno-format-truncation", "-fPIC"]
 
 CORE = ["cli.c", "validate.c", "oracle.c", "bindump.c", "perf.c", "devmap.c"]
 NCCL_TESTS = ["allreduce", "allgather", "allgatherv", "alltoall", "bcast", "gather", "overlap", "pingpong", "reduce",

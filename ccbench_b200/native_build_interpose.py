@@ -23,3 +23,8 @@ def build(verbose: bool = False) -> None:
     ]:
         if src.exists():
             nb.cc(libs / name, [src], shared=True, libs=extra, verbose=verbose)
+    # perf wrapper for the NCCL path: plain cc, no CUDA or NCCL headers
+    perf_src = [root / "userconfig/wrapper_code_examples/perf/perfnccl/perfnccl.c",
+                root / "csrc/wrappers/perf_helper_nccl.c", root / "csrc/core/perf.c"]
+    if all(p.exists() for p in perf_src):
+        nb.cc(libs / "libperfnccl.so", perf_src, shared=True, libs=["-ldl", "-lpthread"], verbose=verbose, compiler="cc")
