@@ -28,9 +28,12 @@ def int8_encode(x: torch.Tensor, group: int = 128):
     """Returns (q int8 [n_pad], scale fp32 [n_pad/group]) for fp32 x (padded with zeros)."""
     xf = _pad_to(x.float(), group).reshape(-1, group)
     m = xf.abs().amax(dim=1, keepdim=True)
-    inv = torch.where(m > 0, 127.0 / m, torch.zeros_like(m))
+    # tensor / tensor so that both quotients are single IEEE divisions like the kernel's
+    # (`127.0 / m` and `m / 127.0` with a Python scalar go through a reciprocal)
+    c127 = torch.full_like(m, 127.0)
+    inv = torch.where(m > 0, c127 / m.clamp_min(torch.finfo(torch.float32).tiny), torch.zeros_like(m))
     q = torch.round(xf * inv).clamp_(-127, 127).to(torch.int8)
-    return q.reshape(-1), (m / 127.0).reshape(-1)
+    return q.reshape(-1), (m / c127).reshape(-1)
 
 
 def int8_decode(q: torch.Tensor, scale: torch.Tensor, group: int = 128) -> torch.Tensor:
@@ -47,7 +50,7 @@ def int8_encode_reference_wire(x: torch.Tensor, group: int = 256):
     is all ~0) followed by the int8 payload."""
     xf = _pad_to(x.float(), group).reshape(-1, group)
     m = xf.abs().amax(dim=1, keepdim=True)
-    inv = torch.where(m < 1e-10, torch.ones_like(m), 127.0 / m)
+    inv = torch.where(m < 1e-10, torch.ones_like(m), torch.full_like(m, 127.0) / m.clamp_min(1e-30))
     q = torch.round(xf * inv).clamp_(-128, 127).to(torch.int8)
     return inv.reshape(-1), q.reshape(-1)[: x.numel()]
 
