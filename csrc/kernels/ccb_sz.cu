@@ -1,0 +1,571 @@
+// SZ-style error-bounded lossy codec for 3-D fp32 fields, and its fusion with
+// AllGather / Broadcast over peer memory.
+//
+// Codec (format "ccb-sz v1"):
+//   1. pre-quantisation   q = rint(x / step), step = 2 eb (1 - 2^-10), corrected by +-1
+//                         where fp32 rounding picked the farther grid point; the bound
+//                         |x - q * step| <= eb is then checked on the very product the
+//                         decoder computes, and a tile that fails it is stored raw;
+//   2. 3-D Lorenzo        d = q - (prediction from the 7 already-coded neighbours),
+//                         computed on the integers, inside a 32 x 8 x 8 tile (values
+//                         outside the tile predict as 0), hence lossless and parallel:
+//                         the decoder undoes it with prefix sums along x, y and z;
+//   3. bit-packing        zig-zag to unsigned, then per row of 32 values the minimum
+//                         width w (0..32) and w bit-planes of 32 bits (warp ballots).
+// A tile is  [64 row widths (1 B each)][bit-planes of row 0][row 1]...  padded to
+// 16 B; a tile whose values do not fit the integer range (or are not finite) is
+// stored raw (width byte 0 = 255, then 8 KiB of fp32). Eight consecutive tiles form a
+// group that owns a fixed-capacity slot of kGroupStride bytes:
+//   [8 x u32 tile sizes][tile 0][tile 1]...
+// so a receiver finds every tile without any size exchange, while only the used
+// bytes are ever written (and cross NVLink).
+//
+// Kernel shape: one thread-block cluster of 8 CTAs per group. Each CTA fetches its
+// tile with ONE 3-D TMA copy (cp.async.bulk.tensor, no multicast) tracked by an
+// mbarrier, packs it in shared memory, the cluster exchanges the 8 sizes through
+// distributed shared memory to place the tiles back to back, and the packed tile is
+// copied out with 16-byte stores, to local memory (ccb_sz_compress) or straight
+// into every peer's arena (ccb_sz_all_gather), where the same CTAs decode what
+// arrives. Fields whose x extent is not a multiple of 4 elements (TMA needs 16-byte
+// row strides) take a plain-load path.
+//
+// The reference has no GPU error-bounded codec: it reaches SZ3 through dlopen on the
+// CPU (userconfig/wrapper_code_examples/compression/sz3/mpi_sz3_wrapper.c:57-101,
+// :138-218) and cuZFP as a library call (zfp_for_gpu_nvidia.cu:130, :179).
+#include <cooperative_groups.h>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <string.h>
+
+#include "../rt/ccb_rt_internal.h"
+#include "ccb/ccb_sz.h"
+#include "ccb_reduce.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace ccb {
+
+constexpr int kTX = 32, kTY = 8, kTZ = 8;
+constexpr int kTileVals = kTX * kTY * kTZ;        // 2048
+constexpr int kRows = kTY * kTZ;                  // 64
+constexpr int kSzThreads = 256;                   // warp = z plane, lane = x
+constexpr int kClusterSize = 8;
+constexpr int kTileCap = kRows + kTileVals * 4;   // 8256 bytes, worst case (w = 32 everywhere)
+constexpr int kGroupHeader = 32;
+constexpr int kGroupStride = kGroupHeader + kClusterSize * kTileCap + 32;  // 66112, multiple of 16
+static_assert(kGroupStride % 16 == 0, "slots must keep 16-byte alignment");
+constexpr float kQMax = 268435456.f;              // 2^28: |q| beyond this stores the tile raw
+
+struct SzField {
+  const float* in;   // compress source (or 0)
+  float* out;        // decompress destination (or 0)
+};
+
+struct SzArgs {
+  CommDev c;
+  CUtensorMap tmap[CCB_MAX_RANKS];   // one per local rank, over `in`
+  SzField f[CCB_MAX_RANKS];          // per local rank
+  unsigned long long* used_bytes;    // per local rank: compressed bytes produced (atomicAdd), or 0
+  char* local_out;                   // compress-only: destination buffer (rank-less)
+  const char* local_in;              // decompress-only: source buffer
+  int nx, ny, nz;
+  int tiles_x, tiles_y, tiles_z;
+  unsigned int ngroups;
+  float eb, two_eb, inv_two_eb;
+  int use_tma;
+  int mode;                          // 0 compress to local_out, 1 decompress from local_in, 2 all-gather, 3 broadcast
+  int root;
+  int rank0, nlocal;
+  unsigned long long slot_bytes;     // arena bytes of one source's slot (ngroups * kGroupStride, rounded)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait on an mbarrier phase: false when the copy never completed.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < (1u << 26); ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar)) : "memory");
+}
+
+struct TileCoord { int x0, y0, z0; };
+__device__ __forceinline__ TileCoord tile_coord(const SzArgs& a, unsigned int tile) {
+  TileCoord t;
+  const unsigned int tx = tile % a.tiles_x, ty = (tile / a.tiles_x) % a.tiles_y, tz = tile / (a.tiles_x * a.tiles_y);
+  t.x0 = tx * kTX; t.y0 = ty * kTY; t.z0 = tz * kTZ;
+  return t;
+}
+
+// Packs the tile held in `vals` (fp32, [z][y][x]) into `pk`; returns its byte size.
+// `qs` is an int view of the same shared buffer (values are overwritten by codes).
+__device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, int* s_scan, int* s_flag, const SzArgs& a) {
+  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
+  int* qs = reinterpret_cast<int*>(vals);
+  int q[kTY];
+  bool bad = false;
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) {
+    const float x = vals[(z * kTY + y) * kTX + lane];
+    const float s = __fmul_rn(x, a.inv_two_eb);
+    if (!(fabsf(s) < kQMax)) bad = true;  // also catches NaN / Inf
+    int qi = __float2int_rn(s);
+    const float half = 0.5f * a.two_eb;
+    const float r = __fmul_rn((float)qi, a.two_eb);  // exactly the decoder's product: no FMA contraction
+    if (x - r > half) ++qi;
+    else if (r - x > half) --qi;
+    // The grid step is a shade under 2 eb (see fill_geometry), which absorbs the rounding
+    // of q * step for |q| < 2^13. Beyond that a value can fall between two grid points
+    // that are both more than eb away: such a tile is stored raw, so the bound always holds.
+    if (fabsf(x - __fmul_rn((float)qi, a.two_eb)) > a.eb) bad = true;
+    q[y] = qi;
+  }
+  if (threadIdx.x == 0) *s_flag = 0;
+  __syncthreads();
+  if (bad) *s_flag = 1;
+  __syncthreads();
+  if (*s_flag) {  // raw tile: marker + the fp32 values
+    for (int i = threadIdx.x; i < kRows; i += kSzThreads) pk[i] = (i == 0) ? 255 : 0;
+    float* raw = reinterpret_cast<float*>(pk + kRows);
+    for (int i = threadIdx.x; i < kTileVals; i += kSzThreads) raw[i] = vals[i];
+    __syncthreads();
+    return kRows + kTileVals * 4;
+  }
+  // codes replace the values in shared memory so that plane z can read plane z-1
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) qs[(z * kTY + y) * kTX + lane] = q[y];
+  __syncthreads();
+  uint32_t plane[kTY];
+  int width[kTY];
+  int prev_a = 0;
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) {
+    const int below = z > 0 ? qs[((z - 1) * kTY + y) * kTX + lane] : 0;
+    const int av = q[y] - below;              // difference along z
+    const int bv = av - prev_a;               // then along y
+    prev_a = av;
+    int left = __shfl_up_sync(0xffffffffu, bv, 1);
+    if (lane == 0) left = 0;
+    const int d = bv - left;                  // then along x
+    const uint32_t u = ((uint32_t)d << 1) ^ (uint32_t)(d >> 31);
+    const uint32_t mx = __reduce_max_sync(0xffffffffu, u);
+    const int w = mx ? 32 - __clz(mx) : 0;
+    width[y] = w;
+    uint32_t mine = 0;
+    for (int j = 0; j < w; ++j) {
+      const uint32_t p = __ballot_sync(0xffffffffu, (u >> j) & 1u);
+      if (lane == j) mine = p;
+    }
+    plane[y] = mine;
+    if (lane == 0) {
+      pk[z * kTY + y] = (unsigned char)w;
+      s_scan[z * kTY + y] = w;
+    }
+  }
+  __syncthreads();
+  // exclusive prefix of the 64 widths (in words)
+  if (threadIdx.x < 32) {
+    int a0 = s_scan[2 * lane], a1 = s_scan[2 * lane + 1];
+    int s = a0 + a1, incl = s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    const int excl = incl - s;
+    s_scan[2 * lane] = excl;
+    s_scan[2 * lane + 1] = excl + a0;
+    if (lane == 31) s_scan[kRows] = incl;
+  }
+  __syncthreads();
+  uint32_t* words = reinterpret_cast<uint32_t*>(pk + kRows);
+#pragma unroll
+  for (int y = 0; y < kTY; ++y)
+    if (lane < width[y]) words[s_scan[z * kTY + y] + lane] = plane[y];
+  const uint32_t bytes = kRows + 4u * (uint32_t)s_scan[kRows];
+  const uint32_t padded = (bytes + 15u) & ~15u;
+  for (uint32_t i = bytes + threadIdx.x; i < padded; i += kSzThreads) pk[i] = 0;
+  __syncthreads();
+  return padded;
+}
+
+// Decodes a packed tile at `src` (global or arena memory) into vals[z][y][x] (fp32, shared).
+__device__ __forceinline__ void unpack_tile(const unsigned char* src, float* vals, int* s_scan, const SzArgs& a) {
+  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
+  if (threadIdx.x < kRows / 4) reinterpret_cast<uint32_t*>(s_scan + kRows + 8)[threadIdx.x] = ldg_cg_u32(src + 4 * threadIdx.x);
+  __syncthreads();
+  const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(s_scan + kRows + 8);
+  if (wbytes[0] == 255) {
+    const float* raw = reinterpret_cast<const float*>(src + kRows);
+    for (int i = threadIdx.x; i < kTileVals; i += kSzThreads) vals[i] = __uint_as_float(ldg_cg_u32(raw + i));
+    __syncthreads();
+    return;
+  }
+  if (threadIdx.x < 32) {
+    int a0 = wbytes[2 * lane], a1 = wbytes[2 * lane + 1];
+    int s = a0 + a1, incl = s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    s_scan[2 * lane] = incl - s;
+    s_scan[2 * lane + 1] = incl - s + a0;
+  }
+  __syncthreads();
+  const uint32_t* words = reinterpret_cast<const uint32_t*>(src + kRows);
+  int* qs = reinterpret_cast<int*>(vals);
+  int run_y = 0;  // prefix along y of the x-prefixed differences
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) {
+    const int row = z * kTY + y;
+    const int w = wbytes[row];
+    const uint32_t mine = lane < w ? ldg_cg_u32(words + s_scan[row] + lane) : 0u;
+    uint32_t u = 0;
+    for (int j = 0; j < w; ++j) u |= ((__shfl_sync(0xffffffffu, mine, j) >> lane) & 1u) << j;
+    int d = (int)(u >> 1) ^ -(int)(u & 1u);
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {  // inclusive prefix along x
+      int t = __shfl_up_sync(0xffffffffu, d, s);
+      if (lane >= s) d += t;
+    }
+    run_y += d;
+    qs[row * kTX + lane] = run_y;
+  }
+  __syncthreads();
+  // prefix along z: every thread sums the planes below its own
+  int acc[kTY];
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) {
+    int s = 0;
+    for (int zz = 0; zz <= z; ++zz) s += qs[(zz * kTY + y) * kTX + lane];
+    acc[y] = s;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) vals[(z * kTY + y) * kTX + lane] = __fmul_rn((float)acc[y], a.two_eb);
+  __syncthreads();
+}
+
+__device__ __forceinline__ void load_tile_plain(const float* in, float* vals, const TileCoord& t, const SzArgs& a) {
+  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) {
+    const int gx = t.x0 + lane, gy = t.y0 + y, gz = t.z0 + z;
+    float v = 0.f;
+    if (gx < a.nx && gy < a.ny && gz < a.nz) v = in[((size_t)gz * a.ny + gy) * a.nx + gx];
+    vals[(z * kTY + y) * kTX + lane] = v;
+  }
+}
+__device__ __forceinline__ void store_tile(float* out, const float* vals, const TileCoord& t, const SzArgs& a) {
+  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) {
+    const int gx = t.x0 + lane, gy = t.y0 + y, gz = t.z0 + z;
+    if (gx < a.nx && gy < a.ny && gz < a.nz) out[((size_t)gz * a.ny + gy) * a.nx + gx] = vals[(z * kTY + y) * kTX + lane];
+  }
+}
+
+__global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ SzArgs a) {
+  __shared__ __align__(128) float vals[kTileVals];
+  __shared__ __align__(16) unsigned char pk[kTileCap + 16];
+  __shared__ int s_scan[kRows + 8 + kRows / 4 + 4];
+  __shared__ int s_flag;
+  __shared__ uint32_t s_size;            // this CTA's packed size, read by the cluster
+  __shared__ __align__(8) uint64_t mbar;
+  __shared__ CtaSync sync;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int k = (int)cluster.block_rank();          // tile within the group
+  const unsigned int cl = blockIdx.x / kClusterSize, ncl = gridDim.x / kClusterSize;
+  const int lr = blockIdx.y, r = a.rank0 + lr, n = a.c.nranks;
+  const int b = blockIdx.x;                         // flag column
+  const unsigned int ntiles = (unsigned)a.tiles_x * a.tiles_y * a.tiles_z;
+  const bool collective = a.mode >= 2;
+  const bool i_send = a.mode == 0 || a.mode == 2 || (a.mode == 3 && r == a.root);
+  const size_t area = CCB_DATA_OFFSET + (size_t)(a.c.epoch & 1u) * a.c.half_bytes;
+  if (threadIdx.x == 0) {
+    sync.fail = 0;
+    mbar_init(&mbar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  uint32_t parity = 0;
+  unsigned long long produced = 0;
+
+  // ------------------------------------------------------------- compress ----
+  if (i_send && a.mode != 1) {
+    const float* in = a.f[lr].in;
+    for (unsigned int g = cl; g < a.ngroups; g += ncl) {
+      const unsigned int tile = g * kClusterSize + k;
+      uint32_t size = 0;
+      if (tile < ntiles) {
+        const TileCoord t = tile_coord(a, tile);
+        if (a.use_tma) {
+          if (threadIdx.x == 0) {
+            // earlier generic-proxy accesses to `vals` must be ordered before the TMA write
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(&mbar, kTileVals * 4);
+            tma_load_3d(vals, &a.tmap[lr], t.x0, t.y0, t.z0, &mbar);
+          }
+          if (!mbar_wait(&mbar, parity)) {  // the copy never landed: report and leave
+            if (threadIdx.x == 0 && a.c.status) atomicOr(a.c.status + CCB_STATUS_FLAGS, CCB_ST_TIMEOUT);
+            sync.fail = 1;
+          }
+          parity ^= 1u;
+        } else {
+          load_tile_plain(in, vals, t, a);
+        }
+        __syncthreads();
+        size = sync.fail ? 0 : pack_tile(vals, pk, s_scan, &s_flag, a);
+      }
+      if (threadIdx.x == 0) s_size = size;
+      cluster.sync();   // all 8 sizes are published in distributed shared memory
+      uint32_t off = 0;
+      for (int j = 0; j < k; ++j) off += *cluster.map_shared_rank(&s_size, j);
+      // copy the packed tile out: to the local buffer, or to every destination's arena
+      auto emit = [&](char* slot_base) {
+        char* grp = slot_base + (size_t)g * kGroupStride;
+        if (threadIdx.x == 0) reinterpret_cast<uint32_t*>(grp)[k] = size;
+        char* dst = grp + kGroupHeader + off;
+        const uint4* s4 = reinterpret_cast<const uint4*>(pk);
+        for (uint32_t i = threadIdx.x; i < size / 16; i += kSzThreads) stg(dst + 16 * i, s4[i]);
+      };
+      if (a.mode == 0) {
+        emit(a.local_out);
+      } else {
+        for (int j = 0; j < n; ++j) emit(a.c.arena[(r + j) % n] + area + (size_t)r * a.slot_bytes);
+      }
+      produced += size;
+      cluster.sync();   // nobody overwrites s_size or pk while a neighbour still reads
+    }
+    if (a.used_bytes && threadIdx.x == 0 && produced) atomicAdd(a.used_bytes + lr, produced + 0ull);
+  }
+  if (a.mode == 0) return;
+
+  // --------------------------------------------------------------- signal ----
+  if (collective) {
+    __syncthreads();
+    if (i_send && threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(a.c.arena[threadIdx.x], 0, r, b), a.c.epoch);
+    const uint32_t srcmask = a.mode == 2 ? 0xffu : (1u << a.root);
+    if (!cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, srcmask, 0xA0)) return;
+  }
+
+  // ------------------------------------------------------------ decompress ---
+  const int nsrc = a.mode == 2 ? n : 1;
+  for (int si = 0; si < nsrc; ++si) {
+    const int q = a.mode == 2 ? (r + si) % n : a.root;
+    const char* slot = a.mode == 1 ? a.local_in : a.c.arena[r] + area + (size_t)q * a.slot_bytes;
+    float* out = a.f[lr].out + (a.mode == 2 ? (size_t)q * a.nx * a.ny * a.nz : 0);
+    for (unsigned int g = cl; g < a.ngroups; g += ncl) {
+      const unsigned int tile = g * kClusterSize + k;
+      if (tile >= ntiles) continue;
+      const char* grp = slot + (size_t)g * kGroupStride;
+      uint32_t off = 0;
+      for (int j = 0; j < k; ++j) off += ldg_cg_u32(grp + 4 * j);
+      unpack_tile(reinterpret_cast<const unsigned char*>(grp + kGroupHeader + off), vals, s_scan, a);
+      store_tile(out, vals, tile_coord(a, tile), a);
+      __syncthreads();
+    }
+  }
+  if (a.mode == 3) end_handshake(sync, a.c, r);
+}
+
+// --------------------------------------------------------------------- host --
+typedef CUresult (*encode_tiled_t)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static encode_tiled_t tensor_map_encoder() {
+  static encode_tiled_t fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<encode_tiled_t>(p);
+    (void)cudaGetLastError();
+  }
+  return fn;
+}
+
+static bool make_tmap(CUtensorMap* m, const float* base, int nx, int ny, int nz) {
+  encode_tiled_t enc = tensor_map_encoder();
+  if (!enc || (nx % 4) != 0 || (reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)nx, (cuuint64_t)ny, (cuuint64_t)nz};
+  cuuint64_t strides[2] = {(cuuint64_t)nx * 4, (cuuint64_t)nx * ny * 4};
+  cuuint32_t box[3] = {kTX, kTY, kTZ};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static void fill_geometry(SzArgs& a, int nx, int ny, int nz, float eb) {
+  a.nx = nx; a.ny = ny; a.nz = nz;
+  a.tiles_x = (nx + kTX - 1) / kTX;
+  a.tiles_y = (ny + kTY - 1) / kTY;
+  a.tiles_z = (nz + kTZ - 1) / kTZ;
+  const unsigned long long tiles = (unsigned long long)a.tiles_x * a.tiles_y * a.tiles_z;
+  a.ngroups = (unsigned int)((tiles + kClusterSize - 1) / kClusterSize);
+  a.eb = eb;
+  a.two_eb = 2.f * eb * (1.f - 0.0009765625f);  // quantisation step: 2 eb (1 - 2^-10)
+  a.inv_two_eb = 1.f / a.two_eb;
+}
+
+// Launch with a cluster of 8 CTAs; cooperative when the kernel waits on peers.
+static int sz_launch(SzArgs& a, int nlocal, int num_sms, bool waits, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = kClusterSize;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kSzThreads, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cfg.attrs = attrs;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(kClusterSize, 1, 1);
+  int max_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, sz_kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+    (void)cudaGetLastError();
+    max_clusters = num_sms / kClusterSize;
+  }
+  // CTAs that wait on peers must all be resident: stay within the resident clusters
+  unsigned int clusters = a.ngroups;
+  const unsigned int cap = (unsigned)(max_clusters / nlocal > 0 ? max_clusters / nlocal : 1);
+  if (clusters > cap) clusters = cap;
+  if (clusters * kClusterSize > CCB_MAX_CTAS) clusters = CCB_MAX_CTAS / kClusterSize;
+  cfg.gridDim = dim3(clusters * kClusterSize, (unsigned)nlocal, 1);
+  if (waits) {
+    attrs[1].id = cudaLaunchAttributeCooperative;
+    attrs[1].val.cooperative = 1;
+    cfg.numAttrs = 2;
+  }
+  cudaError_t e = cudaLaunchKernelEx(&cfg, sz_kernel, a);
+  if (e != cudaSuccess && waits) {  // some drivers refuse cluster + cooperative: the bounded grid still fits
+    (void)cudaGetLastError();
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, sz_kernel, a);
+  }
+  if (e != cudaSuccess) {
+    set_error("sz kernel launch failed: %s", cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  count_launch();
+  return CCB_OK;
+}
+
+static int device_sms() {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return sms;
+}
+
+}  // namespace ccb
+
+using namespace ccb;
+
+extern "C" uint64_t ccb_sz_capacity(int nx, int ny, int nz) {
+  SzArgs a;
+  memset(&a, 0, sizeof(a));
+  fill_geometry(a, nx, ny, nz, 1.f);
+  return (uint64_t)a.ngroups * kGroupStride;
+}
+
+extern "C" int ccb_sz_compress(const float* in, int nx, int ny, int nz, float eb, void* out, unsigned long long* d_used,
+                               ccb_stream_t stream) {
+  if (!in || !out || nx < 1 || ny < 1 || nz < 1 || !(eb > 0.f)) {
+    set_error("ccb_sz_compress: bad arguments");
+    return CCB_ERR_ARG;
+  }
+  SzArgs a;
+  memset(&a, 0, sizeof(a));
+  fill_geometry(a, nx, ny, nz, eb);
+  a.c.nranks = 1;
+  a.f[0].in = in;
+  a.local_out = static_cast<char*>(out);
+  a.used_bytes = d_used;
+  a.use_tma = make_tmap(&a.tmap[0], in, nx, ny, nz) ? 1 : 0;
+  a.mode = 0;
+  a.nlocal = 1;
+  if (d_used) cudaMemsetAsync(d_used, 0, sizeof(unsigned long long), static_cast<cudaStream_t>(stream));
+  return sz_launch(a, 1, device_sms(), false, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ccb_sz_decompress(const void* in, int nx, int ny, int nz, float eb, float* out, ccb_stream_t stream) {
+  if (!in || !out || nx < 1 || ny < 1 || nz < 1 || !(eb > 0.f)) {
+    set_error("ccb_sz_decompress: bad arguments");
+    return CCB_ERR_ARG;
+  }
+  SzArgs a;
+  memset(&a, 0, sizeof(a));
+  fill_geometry(a, nx, ny, nz, eb);
+  a.c.nranks = 1;
+  a.f[0].out = out;
+  a.local_in = static_cast<const char*>(in);
+  a.mode = 1;
+  a.nlocal = 1;
+  return sz_launch(a, 1, device_sms(), false, static_cast<cudaStream_t>(stream));
+}
+
+// Error-bounded AllGather (root < 0) or Broadcast (root >= 0) of one nx*ny*nz field per
+// rank. AllGather: recv holds nranks fields in rank order. d_used (optional, one
+// counter per local rank, device memory) receives the compressed bytes each rank sent
+// to ONE destination.
+extern "C" int ccb_sz_collective(ccb_comm* c, const float* const* send, float* const* recv, int nx, int ny, int nz, float eb,
+                                 int root, unsigned long long* d_used, ccb_stream_t stream_) {
+  int rc = check_alive(c);
+  if (rc) return rc;
+  if (!send || !recv || nx < 1 || ny < 1 || nz < 1 || !(eb > 0.f)) {
+    set_error("ccb_sz_collective: bad arguments");
+    return CCB_ERR_ARG;
+  }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int n = ccb_comm_nranks(c), nlocal = ccb_comm_nlocal(c);
+  SzArgs a;
+  memset(&a, 0, sizeof(a));
+  fill_geometry(a, nx, ny, nz, eb);
+  a.slot_bytes = ((unsigned long long)a.ngroups * kGroupStride + 255ull) & ~255ull;
+  a.c = comm_dev(c, 0);
+  const int nslots = n;
+  if ((unsigned long long)nslots * a.slot_bytes > a.c.half_bytes) {
+    set_error("arena too small: an error-bounded collective of %d x %d x %d needs %llu bytes of staging (CCB_ARENA_MB)", nx, ny, nz,
+              (unsigned long long)nslots * a.slot_bytes * 2 + CCB_DATA_OFFSET);
+    return CCB_ERR_CAPACITY;
+  }
+  a.c = comm_dev(c, next_epoch(c));
+  bool tma = true;
+  for (int i = 0; i < nlocal; ++i) {
+    a.f[i].in = send[i];
+    a.f[i].out = recv[i];
+    const bool sender = root < 0 || (ccb_comm_rank(c) + i) == root;
+    if (sender && !make_tmap(&a.tmap[i], send[i], nx, ny, nz)) tma = false;
+  }
+  a.use_tma = tma ? 1 : 0;
+  a.used_bytes = d_used;
+  a.mode = root < 0 ? 2 : 3;
+  a.root = root < 0 ? 0 : root;
+  a.rank0 = ccb_comm_rank(c);
+  a.nlocal = nlocal;
+  if (d_used) cudaMemsetAsync(d_used, 0, sizeof(unsigned long long) * nlocal, stream);
+  return sz_launch(a, nlocal, device_sms(), true, stream);
+}

@@ -1,0 +1,84 @@
+"""Error-bounded codec: bound, exact agreement with the NumPy restatement, packed
+size, odd shapes (plain-load path), raw tiles, and the fused AllGather / Broadcast with
+all ranks played on one GPU."""
+import numpy as np
+import pytest
+import torch
+
+from ccbench_b200 import Communicator
+from ccbench_b200.models.workloads import smooth_field
+from ccbench_b200.ops import sz
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("shape", [(16, 16, 64), (8, 8, 32), (24, 40, 96), (9, 13, 50), (17, 8, 33)])
+@pytest.mark.parametrize("eb", [1e-3, 1e-1])
+def test_roundtrip_matches_restatement(shape, eb):
+    g = torch.Generator().manual_seed(sum(shape))
+    x = torch.randn(shape, generator=g).cumsum(-1).mul_(0.1)
+    xg = x.cuda()
+    buf, used = sz.compress(xg, eb)
+    out = sz.decompress(buf, shape, eb)
+    torch.cuda.synchronize()
+    recon, nbytes = sz.restate(x.numpy(), eb)
+    assert (out.cpu() - x).abs().max().item() <= float(np.float32(eb))  # the bound is the fp32 value of eb
+    assert np.array_equal(out.cpu().numpy(), recon)
+    assert int(used.item()) == nbytes
+
+
+def test_smooth_field_ratio_and_bound():
+    f = smooth_field(128, seed=1, device="cuda")
+    rng = (f.max() - f.min()).item()
+    eb = 1e-4 * rng
+    buf, used = sz.compress(f, eb)
+    out = sz.decompress(buf, f.shape, eb)
+    torch.cuda.synchronize()
+    assert (out - f).abs().max().item() <= float(np.float32(eb))
+    ratio = f.numel() * 4 / int(used.item())
+    assert ratio > 2.5, ratio
+    mse = ((out - f).double() ** 2).mean().item()
+    psnr = 20 * np.log10(rng) - 10 * np.log10(mse)
+    assert psnr > 80
+
+
+def test_non_finite_and_huge_values_are_stored_raw():
+    x = torch.randn(8, 8, 64)
+    x[0, 0, 0] = float("inf")
+    x[3, 2, 40] = 1e30
+    xg = x.cuda()
+    buf, used = sz.compress(xg, 1e-3)
+    out = sz.decompress(buf, x.shape, 1e-3).cpu()
+    assert out[0, 0, 0] == float("inf") and out[3, 2, 40] == x[3, 2, 40]
+    fin = torch.isfinite(x) & (x.abs() < 1e20)
+    assert (out[fin] - x[fin]).abs().max().item() <= float(np.float32(1e-3))
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_fused_all_gather_and_broadcast(n):
+    shape = (16, 24, 64)
+    comm = Communicator.local(n, arena_bytes=64 << 20)
+    try:
+        g = torch.Generator().manual_seed(n)
+        xs = [torch.randn(shape, generator=g).cumsum(-1).mul_(0.05 * (r + 1)) for r in range(n)]
+        xg = [x.cuda() for x in xs]
+        eb = 1e-3
+        recv = [torch.zeros((n,) + shape, device="cuda") for _ in range(n)]
+        used = torch.zeros(n, dtype=torch.int64, device="cuda")
+        for _ in range(2):
+            sz.all_gather(comm, xg, recv, eb, used)
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0
+        want = np.stack([sz.restate(x.numpy(), eb)[0] for x in xs])
+        for r in range(n):
+            assert np.array_equal(recv[r].cpu().numpy(), want)
+        assert all(int(u) == sz.restate(xs[i].numpy(), eb)[1] for i, u in enumerate(used.tolist()))
+        out = [torch.zeros(shape, device="cuda") for _ in range(n)]
+        for _ in range(3):
+            sz.broadcast(comm, xg, out, eb, root=n - 1)
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0
+        for r in range(n):
+            assert np.array_equal(out[r].cpu().numpy(), want[n - 1])
+    finally:
+        comm.close()
