@@ -1,0 +1,2 @@
+/* Path shim: configs written for the reference layout list this file as a source. */
+#include "../../../../csrc/wrappers/perf_helper_mpi.c"
