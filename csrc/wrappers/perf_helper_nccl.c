@@ -217,3 +217,6 @@ int perf_nccl_local_size(void) {
     for (int r = 0; r < g_nhosts; ++r) c += perf_nccl_is_intra(r);
     return c;
 }
+
+/* the table's time origin is the moment the wrapper library is loaded */
+__attribute__((constructor)) static void perf_early_init(void) { perf_nccl_get_tls(); }
