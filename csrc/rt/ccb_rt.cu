@@ -673,7 +673,10 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
   const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count, &a.tile_warps);
   // Pipeline depth: each wave should still hold a couple of tiles per CTA.
   const size_t tiles_per_cta = ((shard_elems < count ? shard_elems : count) / ((size_t)a.tile_warps * kWarpElems)) / (size_t)ctas;
-  int waves = c->waves > 0 ? c->waves : (tiles_per_cta >= 8 ? 4 : tiles_per_cta >= 4 ? 2 : 1);
+  // Measured on B200: each extra wave costs a pipeline drain (fence + flag round trip) that
+  // outweighs the overlap it buys, so the default is one wave; the knob stays for tuning.
+  int waves = c->waves > 0 ? c->waves : 1;
+  (void)tiles_per_cta;
   if (waves > CCB_MAX_SLOTS / 2) waves = CCB_MAX_SLOTS / 2;
   a.waves = shape == kTwoShot ? waves : 1;
   return launch(c, fn, ctas, &a, stream);
@@ -745,10 +748,17 @@ extern "C" int ccb_all_reduce(ccb_comm* c, const void* const* send, void* const*
   const int n = c->nranks;
   const size_t es = elem_size(dtype);
   if (algo == CCB_ALGO_AUTO) {
-    // One-shot moves n times the bytes but has one exchange instead of two: it wins
-    // while the message is latency-bound.
-    algo = (count * es <= (size_t)env_u64("CCB_ONESHOT_MAX_BYTES", 256 << 10) || n == 1) ? CCB_ALGO_ONESHOT : CCB_ALGO_TWOSHOT;
-    if (n == 1) algo = CCB_ALGO_TWOSHOT;
+    // One-shot has one exchange instead of two (about 10 us less latency) but every rank
+    // sends its whole message to every peer: (n-1) * S wire bytes against 2(n-1)/n * S.
+    // It wins while the extra (n-1)(1-2/n) * S bytes cost less than that latency at the
+    // ~600 GB/s an SM-driven NVLink stream sustains, i.e. below about
+    // 6 MB / ((n-1)(1-2/n)) of wire bytes; with two ranks both shapes move the same
+    // bytes and one-shot stays ahead until its n-way local reduction dominates (32 MiB).
+    const size_t wire = codec_slot_bytes(codec, dtype, round_up(count, kWarpElems));
+    size_t limit = n <= 2 ? ((size_t)32 << 20) : (size_t)(6.0e6 / ((n - 1) * (1.0 - 2.0 / n)));
+    limit = (size_t)env_u64("CCB_ONESHOT_MAX_BYTES", limit);
+    const bool fits = (size_t)n * wire <= c->half_bytes;
+    algo = (n > 1 && fits && wire <= limit) ? CCB_ALGO_ONESHOT : CCB_ALGO_TWOSHOT;
   }
   if (algo == CCB_ALGO_NVLS) return nvls_all_reduce(c, send, recv, count, dtype, op, stream);
   if (algo == CCB_ALGO_RING || algo == CCB_ALGO_TREE) {
