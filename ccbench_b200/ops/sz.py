@@ -1,4 +1,4 @@
-"""Python face of the error-bounded codec (ccb-sz v1) plus a NumPy restatement of its
+"""Python face of the error-bounded codec (ccb-sz v2) plus a NumPy restatement of its
 arithmetic used as the test oracle: the reconstruction q * 2eb and the packed size
 must match the kernel's exactly."""
 from __future__ import annotations
@@ -92,7 +92,8 @@ def restate(field: np.ndarray, eb: float):
     d3 = d2.copy()
     d3[..., :, :, 1:] -= d2[..., :, :, :-1]
     u = ((d3 << 1) ^ (d3 >> 63)).astype(np.uint64) & np.uint64(0xFFFFFFFF)
-    mx = u.max(axis=-1)  # per row of 32
+    # a packing row is element e (of 8 consecutive x) over the 8 lines x 4 segments of a plane
+    mx = u.reshape(u.shape[:-2] + (TY, TX // 8, 8)).max(axis=(-2, -3))  # [..., z, e]
     w = np.where(mx > 0, np.floor(np.log2(np.maximum(mx, 1).astype(np.float64))).astype(np.int64) + 1, 0)
     tile_bytes = 64 + 4 * w.sum(axis=(-1, -2))
     tile_bytes = (tile_bytes + 15) // 16 * 16

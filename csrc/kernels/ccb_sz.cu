@@ -1,7 +1,7 @@
 // SZ-style error-bounded lossy codec for 3-D fp32 fields, and its fusion with
 // AllGather / Broadcast over peer memory.
 //
-// Codec (format "ccb-sz v1"):
+// Codec (format "ccb-sz v2"):
 //   1. pre-quantisation   q = rint(x / step), step = 2 eb (1 - 2^-10), corrected by +-1
 //                         where fp32 rounding picked the farther grid point; the bound
 //                         |x - q * step| <= eb is then checked on the very product the
@@ -10,8 +10,13 @@
 //                         computed on the integers, inside a 32 x 8 x 8 tile (values
 //                         outside the tile predict as 0), hence lossless and parallel:
 //                         the decoder undoes it with prefix sums along x, y and z;
-//   3. bit-packing        zig-zag to unsigned, then per row of 32 values the minimum
-//                         width w (0..32) and w bit-planes of 32 bits (warp ballots).
+//   3. bit-packing        zig-zag to unsigned, then per packing row of 32 values the
+//                         minimum width w (0..32) and w bit-planes of 32 bits. A row is
+//                         element e of the eight consecutive x that each of the 32 threads
+//                         of a z plane owns (thread = 4 y + x / 8): row index 8 z + e, bit
+//                         t of a plane belongs to thread t. Planes come out of a 32 x 32
+//                         bit-matrix transpose across the warp (five shuffle steps), one
+//                         transpose for FOUR rows when their widths are at most 8 bits.
 // A tile is  [64 row widths (1 B each)][bit-planes of row 0][row 1]...  padded to
 // 16 B; a tile whose values do not fit the integer range (or are not finite) is
 // stored raw (width byte 0 = 255, then 8 KiB of fp32). Eight consecutive tiles form a
@@ -54,7 +59,7 @@ constexpr int kTileCap = kRows + kTileVals * 4;   // 8256 bytes, worst case (w =
 constexpr int kGroupHeader = 32;
 constexpr int kGroupStride = kGroupHeader + kClusterSize * kTileCap + 32;  // 66112, multiple of 16
 static_assert(kGroupStride % 16 == 0, "slots must keep 16-byte alignment");
-constexpr float kQMax = 268435456.f;              // 2^28: |q| beyond this stores the tile raw
+constexpr float kQMax = 4194304.f;                // 2^22: |q| beyond this stores the tile raw
 
 struct SzField {
   const float* in;   // compress source (or 0)
@@ -114,154 +119,223 @@ __device__ __forceinline__ TileCoord tile_coord(const SzArgs& a, unsigned int ti
   return t;
 }
 
-// Packs the tile held in `vals` (fp32, [z][y][x]) into `pk`; returns its byte size.
-// `qs` is an int view of the same shared buffer (values are overwritten by codes).
-__device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, int* s_scan, int* s_flag, const SzArgs& a) {
-  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
-  int* qs = reinterpret_cast<int*>(vals);
-  int q[kTY];
-  bool bad = false;
+// Thread mapping of both directions: warp = z plane of the tile, lane = 4 y + xq, and the
+// thread owns the eight consecutive values x = 8 xq .. 8 xq + 7 of line (y, z), which sit at
+// words 8 * threadIdx.x .. +7 of the tile in shared memory (two 16-byte accesses). A packing
+// row is element e of all 32 lanes of a warp: row index 8 z + e.
+
+// Transposes the 32 x 32 bit matrix whose row i is the word held by lane i: afterwards
+// lane j holds column j (bit i of the result = bit j of lane i's input). Five exchange steps.
+__device__ __forceinline__ uint32_t transpose32(uint32_t x, int lane) {
 #pragma unroll
-  for (int y = 0; y < kTY; ++y) {
-    const float x = vals[(z * kTY + y) * kTX + lane];
-    const float s = __fmul_rn(x, a.inv_two_eb);
-    if (!(fabsf(s) < kQMax)) bad = true;  // also catches NaN / Inf
-    int qi = __float2int_rn(s);
-    const float half = 0.5f * a.two_eb;
-    const float r = __fmul_rn((float)qi, a.two_eb);  // exactly the decoder's product: no FMA contraction
-    if (x - r > half) ++qi;
-    else if (r - x > half) --qi;
-    // The grid step is a shade under 2 eb (see fill_geometry), which absorbs the rounding
-    // of q * step for |q| < 2^13. Beyond that a value can fall between two grid points
-    // that are both more than eb away: such a tile is stored raw, so the bound always holds.
-    if (fabsf(x - __fmul_rn((float)qi, a.two_eb)) > a.eb) bad = true;
-    q[y] = qi;
+  for (int s = 16; s >= 1; s >>= 1) {
+    const uint32_t m = s == 16 ? 0x0000ffffu : s == 8 ? 0x00ff00ffu : s == 4 ? 0x0f0f0f0fu : s == 2 ? 0x33333333u : 0x55555555u;
+    const uint32_t p = __shfl_xor_sync(0xffffffffu, x, s);
+    const bool up = (lane & s) != 0;
+    const uint32_t moved = up ? (p >> s) : (p << s);
+    const uint32_t keep = up ? ~m : m;
+    x = (x & keep) | (moved & ~keep);
   }
-  if (threadIdx.x == 0) *s_flag = 0;
-  __syncthreads();
-  if (bad) *s_flag = 1;
-  __syncthreads();
-  if (*s_flag) {  // raw tile: marker + the fp32 values
+  return x;
+}
+__device__ __forceinline__ uint32_t bytesum(uint32_t v) { return __dp4a(v, 0x01010101u, 0u); }
+// True when every byte of w (each at most 32) is at most 8 / at most 16.
+__device__ __forceinline__ bool bytes_le8(uint32_t w) { return ((w + 0x77777777u) & 0x80808080u) == 0; }
+__device__ __forceinline__ bool bytes_le16(uint32_t w) { return ((w + 0x6f6f6f6fu) & 0x80808080u) == 0; }
+
+// Bit-planes of four rows: `W` holds their widths (one byte each), `off` is the word offset
+// of the first row's planes. With all widths <= 8 the four rows share ONE bit-matrix
+// transpose (lane 8 r + j ends up with plane j of row r); widths up to 16 take two, wider
+// rows one transpose each. The byte layout does not depend on which way was taken.
+template <bool kStore>
+__device__ __forceinline__ void planes4(uint32_t (&u)[4], uint32_t W, uint32_t off, uint32_t* words, int lane) {
+  auto pass = [&](int bits, int first_row, int rows) {   // rows * bits == 32
+    const int rr = lane / bits, jj = lane % bits, row = first_row + rr;
+    const uint32_t w = (W >> (8 * row)) & 0xffu;
+    const uint32_t at = off + bytesum(W & ((1u << (8 * row)) - 1u)) + jj;
+    if (kStore) {
+      uint32_t U = 0;
+      for (int r2 = 0; r2 < rows; ++r2) U |= u[first_row + r2] << (bits * r2);
+      const uint32_t X = transpose32(U, lane);
+      if ((uint32_t)jj < w) words[at] = X;
+    } else {
+      const uint32_t X = (uint32_t)jj < w ? ldg_cg_u32(words + at) : 0u;
+      const uint32_t U = transpose32(X, lane);
+      for (int r2 = 0; r2 < rows; ++r2) u[first_row + r2] = bits == 32 ? U : (U >> (bits * r2)) & ((1u << bits) - 1u);
+    }
+  };
+  if (bytes_le8(W)) {
+    pass(8, 0, 4);
+  } else if (bytes_le16(W)) {
+    pass(16, 0, 2);
+    pass(16, 2, 2);
+  } else {
+#pragma unroll
+    for (int r2 = 0; r2 < 4; ++r2) pass(32, r2, 1);
+  }
+}
+
+constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23: adding and subtracting it rounds to nearest even
+
+// Packs the tile held in `vals` (fp32, [z][y][x]) into `pk`; returns its byte size.
+// The codes overwrite the values in shared memory (each thread its own eight words).
+__device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, int* s_tot, const SzArgs& a) {
+  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
+  int4* q4 = reinterpret_cast<int4*>(vals) + 2 * threadIdx.x;
+  float x[8];
+  {
+    const float4 v0 = reinterpret_cast<const float4*>(q4)[0], v1 = reinterpret_cast<const float4*>(q4)[1];
+    x[0] = v0.x; x[1] = v0.y; x[2] = v0.z; x[3] = v0.w; x[4] = v1.x; x[5] = v1.y; x[6] = v1.z; x[7] = v1.w;
+  }
+  int q[8];
+  bool bad = false;
+  const float half = 0.5f * a.two_eb;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float s = __fmul_rn(x[e], a.inv_two_eb);
+    bad |= !(fabsf(s) < kQMax);  // also catches NaN / Inf
+    float rf = __fadd_rn(__fadd_rn(s, kRoundMagic), -kRoundMagic);
+    const float diff = __fsub_rn(x[e], __fmul_rn(rf, a.two_eb));  // against the decoder's own product (no FMA)
+    rf += diff > half ? 1.f : 0.f;                                // fp32 rounding picked the farther grid point
+    rf -= -diff > half ? 1.f : 0.f;
+    // The grid step is a shade under 2 eb, which absorbs the rounding of q * step for
+    // |q| < 2^13. Beyond that a value can fall between two grid points that are both more
+    // than eb away: such a tile is stored raw, so the bound always holds.
+    bad |= fabsf(__fsub_rn(x[e], __fmul_rn(rf, a.two_eb))) > a.eb;
+    q[e] = (int)rf;
+  }
+  if (__syncthreads_or(bad)) {  // raw tile: marker + the fp32 values
     for (int i = threadIdx.x; i < kRows; i += kSzThreads) pk[i] = (i == 0) ? 255 : 0;
     float* raw = reinterpret_cast<float*>(pk + kRows);
     for (int i = threadIdx.x; i < kTileVals; i += kSzThreads) raw[i] = vals[i];
     __syncthreads();
     return kRows + kTileVals * 4;
   }
-  // codes replace the values in shared memory so that plane z can read plane z-1
-#pragma unroll
-  for (int y = 0; y < kTY; ++y) qs[(z * kTY + y) * kTX + lane] = q[y];
+  q4[0] = make_int4(q[0], q[1], q[2], q[3]);
+  q4[1] = make_int4(q[4], q[5], q[6], q[7]);
   __syncthreads();
-  uint32_t plane[kTY];
-  int width[kTY];
-  int prev_a = 0;
+  // Lorenzo residual = the three first differences, in any order: z through shared memory
+  // (plane z - 1 belongs to the warp below), y through the lane four below, x in registers.
+  if (z > 0) {
+    const int4 b0 = q4[-64], b1 = q4[-63];
+    q[0] -= b0.x; q[1] -= b0.y; q[2] -= b0.z; q[3] -= b0.w; q[4] -= b1.x; q[5] -= b1.y; q[6] -= b1.z; q[7] -= b1.w;
+  }
 #pragma unroll
-  for (int y = 0; y < kTY; ++y) {
-    const int below = z > 0 ? qs[((z - 1) * kTY + y) * kTX + lane] : 0;
-    const int av = q[y] - below;              // difference along z
-    const int bv = av - prev_a;               // then along y
-    prev_a = av;
-    int left = __shfl_up_sync(0xffffffffu, bv, 1);
-    if (lane == 0) left = 0;
-    const int d = bv - left;                  // then along x
-    const uint32_t u = ((uint32_t)d << 1) ^ (uint32_t)(d >> 31);
-    const uint32_t mx = __reduce_max_sync(0xffffffffu, u);
-    const int w = mx ? 32 - __clz(mx) : 0;
-    width[y] = w;
-    uint32_t mine = 0;
-    for (int j = 0; j < w; ++j) {
-      const uint32_t p = __ballot_sync(0xffffffffu, (u >> j) & 1u);
-      if (lane == j) mine = p;
-    }
-    plane[y] = mine;
-    if (lane == 0) {
-      pk[z * kTY + y] = (unsigned char)w;
-      s_scan[z * kTY + y] = w;
-    }
+  for (int e = 0; e < 8; ++e) {
+    const int up = __shfl_up_sync(0xffffffffu, q[e], 4);
+    q[e] -= lane >= 4 ? up : 0;
+  }
+  int left = __shfl_up_sync(0xffffffffu, q[7], 1);
+  if ((lane & 3) == 0) left = 0;
+  uint32_t u[8], W[2] = {0u, 0u};
+#pragma unroll
+  for (int e = 7; e >= 0; --e) {
+    const int d = q[e] - (e ? q[e - 1] : left);
+    u[e] = ((uint32_t)d << 1) ^ (uint32_t)(d >> 31);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const uint32_t any = __reduce_or_sync(0xffffffffu, u[e]);
+    W[e >> 2] |= (uint32_t)(32 - __clz(any)) << (8 * (e & 3));
+  }
+  const uint32_t tot_lo = bytesum(W[0]), tot = tot_lo + bytesum(W[1]);
+  if (lane == 0) {
+    reinterpret_cast<uint2*>(pk)[z] = make_uint2(W[0], W[1]);   // the eight width bytes of this plane
+    s_tot[z] = (int)tot;
   }
   __syncthreads();
-  // exclusive prefix of the 64 widths (in words)
-  if (threadIdx.x < 32) {
-    int a0 = s_scan[2 * lane], a1 = s_scan[2 * lane + 1];
-    int s = a0 + a1, incl = s;
+  uint32_t base = 0, total = 0;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      int t = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += t;
-    }
-    const int excl = incl - s;
-    s_scan[2 * lane] = excl;
-    s_scan[2 * lane + 1] = excl + a0;
-    if (lane == 31) s_scan[kRows] = incl;
+  for (int zz = 0; zz < kTZ; ++zz) {
+    const uint32_t t = (uint32_t)s_tot[zz];
+    base += zz < z ? t : 0u;
+    total += t;
   }
-  __syncthreads();
   uint32_t* words = reinterpret_cast<uint32_t*>(pk + kRows);
-#pragma unroll
-  for (int y = 0; y < kTY; ++y)
-    if (lane < width[y]) words[s_scan[z * kTY + y] + lane] = plane[y];
-  const uint32_t bytes = kRows + 4u * (uint32_t)s_scan[kRows];
+  uint32_t ua[4] = {u[0], u[1], u[2], u[3]}, ub[4] = {u[4], u[5], u[6], u[7]};
+  planes4<true>(ua, W[0], base, words, lane);
+  planes4<true>(ub, W[1], base + tot_lo, words, lane);
+  const uint32_t bytes = kRows + 4u * total;
   const uint32_t padded = (bytes + 15u) & ~15u;
   for (uint32_t i = bytes + threadIdx.x; i < padded; i += kSzThreads) pk[i] = 0;
   __syncthreads();
   return padded;
 }
 
-// Decodes a packed tile at `src` (global or arena memory) into vals[z][y][x] (fp32, shared).
-__device__ __forceinline__ void unpack_tile(const unsigned char* src, float* vals, int* s_scan, const SzArgs& a) {
+// Decodes a packed tile at `src` (global or arena memory) and writes it to its place in `out`;
+// `qs` is 8 KB of shared scratch.
+__device__ __forceinline__ void unpack_tile(const unsigned char* src, int* qs, const SzArgs& a, float* out, const TileCoord& t) {
   const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
-  if (threadIdx.x < kRows / 4) reinterpret_cast<uint32_t*>(s_scan + kRows + 8)[threadIdx.x] = ldg_cg_u32(src + 4 * threadIdx.x);
-  __syncthreads();
-  const unsigned char* wbytes = reinterpret_cast<const unsigned char*>(s_scan + kRows + 8);
-  if (wbytes[0] == 255) {
+  // the 16 words of row widths, one per lane, and their running word count
+  const uint32_t hw = lane < 16 ? ldg_cg_u32(src + 4 * lane) : 0u;
+  if ((__shfl_sync(0xffffffffu, hw, 0) & 0xffu) == 255u) {
     const float* raw = reinterpret_cast<const float*>(src + kRows);
-    for (int i = threadIdx.x; i < kTileVals; i += kSzThreads) vals[i] = __uint_as_float(ldg_cg_u32(raw + i));
-    __syncthreads();
+    for (int i = threadIdx.x; i < kTileVals; i += kSzThreads) {
+      const int gx = t.x0 + (i % kTX), gy = t.y0 + (i / kTX) % kTY, gz = t.z0 + i / (kTX * kTY);
+      if (gx < a.nx && gy < a.ny && gz < a.nz)
+        out[((size_t)gz * a.ny + gy) * a.nx + gx] = __uint_as_float(ldg_cg_u32(raw + i));
+    }
     return;
   }
-  if (threadIdx.x < 32) {
-    int a0 = wbytes[2 * lane], a1 = wbytes[2 * lane + 1];
-    int s = a0 + a1, incl = s;
+  const uint32_t mine = bytesum(hw);
+  uint32_t incl = mine;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      int t = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += t;
+  for (int d = 1; d < 16; d <<= 1) {
+    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += v;
+  }
+  const uint32_t W0 = __shfl_sync(0xffffffffu, hw, 2 * z), W1 = __shfl_sync(0xffffffffu, hw, 2 * z + 1);
+  const uint32_t base = __shfl_sync(0xffffffffu, incl - mine, 2 * z);
+  uint32_t* words = reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(src) + kRows);
+  uint32_t ua[4], ub[4];
+  planes4<false>(ua, W0, base, words, lane);
+  planes4<false>(ub, W1, base + bytesum(W0), words, lane);
+  int p[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const uint32_t u = e < 4 ? ua[e & 3] : ub[e & 3];
+    const int d = (int)(u >> 1) ^ -(int)(u & 1u);
+    p[e] = e ? p[e - 1] + d : d;          // prefix along x inside the thread
+  }
+  {
+    int sum = p[7];                         // then across the four threads of the line
+    int v = __shfl_up_sync(0xffffffffu, sum, 1);
+    if ((lane & 3) >= 1) sum += v;
+    v = __shfl_up_sync(0xffffffffu, sum, 2);
+    if ((lane & 3) >= 2) sum += v;
+    const int before = sum - p[7];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) p[e] += before;
+  }
+  int4* q4 = reinterpret_cast<int4*>(qs) + 2 * threadIdx.x;
+  q4[0] = make_int4(p[0], p[1], p[2], p[3]);
+  q4[1] = make_int4(p[4], p[5], p[6], p[7]);
+  __syncthreads();
+  // prefix along y: threads re-mapped to (x = lane, z = warp) walk the eight lines of their plane
+  {
+    int run = 0;
+#pragma unroll
+    for (int y = 0; y < kTY; ++y) {
+      run += qs[(z * kTY + y) * kTX + lane];
+      qs[(z * kTY + y) * kTX + lane] = run;
     }
-    s_scan[2 * lane] = incl - s;
-    s_scan[2 * lane + 1] = incl - s + a0;
   }
   __syncthreads();
-  const uint32_t* words = reinterpret_cast<const uint32_t*>(src + kRows);
-  int* qs = reinterpret_cast<int*>(vals);
-  int run_y = 0;  // prefix along y of the x-prefixed differences
+  // prefix along z: threads re-mapped to (x = lane, y = warp) walk z with a running sum and
+  // write each reconstructed row straight to the field (coalesced 128-byte row stores)
+  {
+    const int y = z;  // this warp now owns line y of every plane
+    const int gx = t.x0 + lane, gy = t.y0 + y;
+    const bool ok = gx < a.nx && gy < a.ny;
+    int run = 0;
 #pragma unroll
-  for (int y = 0; y < kTY; ++y) {
-    const int row = z * kTY + y;
-    const int w = wbytes[row];
-    const uint32_t mine = lane < w ? ldg_cg_u32(words + s_scan[row] + lane) : 0u;
-    uint32_t u = 0;
-    for (int j = 0; j < w; ++j) u |= ((__shfl_sync(0xffffffffu, mine, j) >> lane) & 1u) << j;
-    int d = (int)(u >> 1) ^ -(int)(u & 1u);
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) {  // inclusive prefix along x
-      int t = __shfl_up_sync(0xffffffffu, d, s);
-      if (lane >= s) d += t;
+    for (int zz = 0; zz < kTZ; ++zz) {
+      run += qs[(zz * kTY + y) * kTX + lane];
+      const int gz = t.z0 + zz;
+      if (ok && gz < a.nz) out[((size_t)gz * a.ny + gy) * a.nx + gx] = __fmul_rn((float)run, a.two_eb);
     }
-    run_y += d;
-    qs[row * kTX + lane] = run_y;
   }
-  __syncthreads();
-  // prefix along z: every thread sums the planes below its own
-  int acc[kTY];
-#pragma unroll
-  for (int y = 0; y < kTY; ++y) {
-    int s = 0;
-    for (int zz = 0; zz <= z; ++zz) s += qs[(zz * kTY + y) * kTX + lane];
-    acc[y] = s;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int y = 0; y < kTY; ++y) vals[(z * kTY + y) * kTX + lane] = __fmul_rn((float)acc[y], a.two_eb);
-  __syncthreads();
+  __syncthreads();   // the scratch is free for the next tile
 }
 
 __device__ __forceinline__ void load_tile_plain(const float* in, float* vals, const TileCoord& t, const SzArgs& a) {
@@ -274,23 +348,14 @@ __device__ __forceinline__ void load_tile_plain(const float* in, float* vals, co
     vals[(z * kTY + y) * kTX + lane] = v;
   }
 }
-__device__ __forceinline__ void store_tile(float* out, const float* vals, const TileCoord& t, const SzArgs& a) {
-  const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
-#pragma unroll
-  for (int y = 0; y < kTY; ++y) {
-    const int gx = t.x0 + lane, gy = t.y0 + y, gz = t.z0 + z;
-    if (gx < a.nx && gy < a.ny && gz < a.nz) out[((size_t)gz * a.ny + gy) * a.nx + gx] = vals[(z * kTY + y) * kTX + lane];
-  }
-}
-
 __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ SzArgs a) {
-  __shared__ __align__(128) float vals[kTileVals];
+  __shared__ __align__(128) float vals2[2][kTileVals];   // two landing buffers: the next tile is in flight
   __shared__ __align__(16) unsigned char pk[kTileCap + 16];
   __shared__ int s_scan[kRows + 8 + kRows / 4 + 4];
-  __shared__ int s_flag;
-  __shared__ uint32_t s_size;            // this CTA's packed size, read by the cluster
-  __shared__ __align__(8) uint64_t mbar;
+  __shared__ uint32_t s_size[2];         // this CTA's packed size per group parity, read by the cluster
+  __shared__ __align__(8) uint64_t mbar[2];
   __shared__ CtaSync sync;
+  float* vals = vals2[0];
 
   cg::cluster_group cluster = cg::this_cluster();
   const int k = (int)cluster.block_rank();          // tile within the group
@@ -303,43 +368,54 @@ __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ 
   const size_t area = CCB_DATA_OFFSET + (size_t)(a.c.epoch & 1u) * a.c.half_bytes;
   if (threadIdx.x == 0) {
     sync.fail = 0;
-    mbar_init(&mbar, 1);
+    mbar_init(&mbar[0], 1);
+    mbar_init(&mbar[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  uint32_t parity = 0;
   unsigned long long produced = 0;
 
   // ------------------------------------------------------------- compress ----
   if (i_send && a.mode != 1) {
     const float* in = a.f[lr].in;
-    for (unsigned int g = cl; g < a.ngroups; g += ncl) {
+    // one thread starts the copy of this CTA's tile of group g into landing buffer `slot`
+    auto prefetch = [&](unsigned int g, int slot) {
+      const unsigned int tile = g * kClusterSize + k;
+      if (!a.use_tma || g >= a.ngroups || tile >= ntiles || threadIdx.x != 0) return;
+      const TileCoord t = tile_coord(a, tile);
+      // earlier generic-proxy accesses to the buffer must be ordered before the TMA write
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      mbar_expect_tx(&mbar[slot], kTileVals * 4);
+      tma_load_3d(vals2[slot], &a.tmap[lr], t.x0, t.y0, t.z0, &mbar[slot]);
+    };
+    prefetch(cl, 0);
+    uint32_t it = 0;
+    for (unsigned int g = cl; g < a.ngroups; g += ncl, ++it) {
+      const int slot = it & 1;
       const unsigned int tile = g * kClusterSize + k;
       uint32_t size = 0;
+      prefetch(g + ncl, slot ^ 1);   // that buffer was released by the __syncthreads ending the previous pack
       if (tile < ntiles) {
         const TileCoord t = tile_coord(a, tile);
+        float* cur = vals2[slot];
         if (a.use_tma) {
-          if (threadIdx.x == 0) {
-            // earlier generic-proxy accesses to `vals` must be ordered before the TMA write
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(&mbar, kTileVals * 4);
-            tma_load_3d(vals, &a.tmap[lr], t.x0, t.y0, t.z0, &mbar);
-          }
-          if (!mbar_wait(&mbar, parity)) {  // the copy never landed: report and leave
+          if (!mbar_wait(&mbar[slot], (it >> 1) & 1u)) {  // the copy never landed: report and leave
             if (threadIdx.x == 0 && a.c.status) atomicOr(a.c.status + CCB_STATUS_FLAGS, CCB_ST_TIMEOUT);
             sync.fail = 1;
           }
-          parity ^= 1u;
         } else {
-          load_tile_plain(in, vals, t, a);
+          load_tile_plain(in, cur, t, a);
         }
         __syncthreads();
-        size = sync.fail ? 0 : pack_tile(vals, pk, s_scan, &s_flag, a);
+        size = sync.fail ? 0 : pack_tile(cur, pk, s_scan, a);
       }
-      if (threadIdx.x == 0) s_size = size;
-      cluster.sync();   // all 8 sizes are published in distributed shared memory
+      if (threadIdx.x == 0) s_size[slot] = size;
+      // One cluster barrier per group: the sizes of group parity `slot` are rewritten only
+      // two groups later, after every CTA has passed the next barrier, by which time all
+      // reads of this group's sizes are done.
+      cluster.sync();
       uint32_t off = 0;
-      for (int j = 0; j < k; ++j) off += *cluster.map_shared_rank(&s_size, j);
+      for (int j = 0; j < k; ++j) off += *cluster.map_shared_rank(&s_size[slot], j);
       // copy the packed tile out: to the local buffer, or to every destination's arena
       auto emit = [&](char* slot_base) {
         char* grp = slot_base + (size_t)g * kGroupStride;
@@ -354,8 +430,9 @@ __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ 
         for (int j = 0; j < n; ++j) emit(a.c.arena[(r + j) % n] + area + (size_t)r * a.slot_bytes);
       }
       produced += size;
-      cluster.sync();   // nobody overwrites s_size or pk while a neighbour still reads
+      __syncthreads();   // pk is free again
     }
+    cluster.sync();      // nobody leaves (or moves on) while a neighbour may still read its sizes
     if (a.used_bytes && threadIdx.x == 0 && produced) atomicAdd(a.used_bytes + lr, produced + 0ull);
   }
   if (a.mode == 0) return;
@@ -378,11 +455,10 @@ __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ 
       const unsigned int tile = g * kClusterSize + k;
       if (tile >= ntiles) continue;
       const char* grp = slot + (size_t)g * kGroupStride;
-      uint32_t off = 0;
-      for (int j = 0; j < k; ++j) off += ldg_cg_u32(grp + 4 * j);
-      unpack_tile(reinterpret_cast<const unsigned char*>(grp + kGroupHeader + off), vals, s_scan, a);
-      store_tile(out, vals, tile_coord(a, tile), a);
-      __syncthreads();
+      const int ln = threadIdx.x & 31;   // sizes of the tiles before this one, one per lane
+      const uint32_t off = __reduce_add_sync(0xffffffffu, ln < k ? ldg_cg_u32(grp + 4 * ln) : 0u);
+      unpack_tile(reinterpret_cast<const unsigned char*>(grp + kGroupHeader + off), reinterpret_cast<int*>(vals), a, out,
+                  tile_coord(a, tile));
     }
   }
   if (a.mode == 3) end_handshake(sync, a.c, r);

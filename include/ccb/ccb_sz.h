@@ -1,4 +1,4 @@
-/* SZ-style error-bounded lossy codec for 3-D fp32 fields ("ccb-sz v1": pre-quantise
+/* SZ-style error-bounded lossy codec for 3-D fp32 fields ("ccb-sz v2": pre-quantise
  * under an absolute bound, 3-D Lorenzo prediction on the integers inside 32x8x8
  * tiles, per-row bit-plane packing) and its fusion with AllGather / Broadcast.
  * Fields are [nz][ny][nx] with x fastest. The format and the kernels are described
