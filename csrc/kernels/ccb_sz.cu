@@ -348,14 +348,24 @@ __device__ __forceinline__ void load_tile_plain(const float* in, float* vals, co
     vals[(z * kTY + y) * kTX + lane] = v;
   }
 }
-__global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ SzArgs a) {
-  __shared__ __align__(128) float vals2[2][kTileVals];   // two landing buffers: the next tile is in flight
-  __shared__ __align__(16) unsigned char pk[kTileCap + 16];
-  __shared__ int s_scan[kRows + 8 + kRows / 4 + 4];
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+constexpr int kStage = kTileCap + 16;   // one packed tile, 16-byte granular
+
+// kKind: 0 compress into a local buffer, 1 decompress from one, 2 the collectives (mode 2
+// all-gather, 3 broadcast). One body, three instantiations, so that each direction gets its
+// own register allocation and occupancy.
+template <int kKind>
+__global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(const __grid_constant__ SzArgs a) {
+  const int mode = kKind == 2 ? a.mode : kKind;
+  // Two 8 KB buffers: compress lands the next tile in one while the other is packed;
+  // decompress prefixes in vals2[0].
+  __shared__ __align__(128) float vals2[2][kTileVals];
+  __shared__ __align__(16) unsigned char pk2[2][kStage];
+  __shared__ int s_tot[kTZ];
   __shared__ uint32_t s_size[2];         // this CTA's packed size per group parity, read by the cluster
   __shared__ __align__(8) uint64_t mbar[2];
   __shared__ CtaSync sync;
-  float* vals = vals2[0];
 
   cg::cluster_group cluster = cg::this_cluster();
   const int k = (int)cluster.block_rank();          // tile within the group
@@ -363,8 +373,8 @@ __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ 
   const int lr = blockIdx.y, r = a.rank0 + lr, n = a.c.nranks;
   const int b = blockIdx.x;                         // flag column
   const unsigned int ntiles = (unsigned)a.tiles_x * a.tiles_y * a.tiles_z;
-  const bool collective = a.mode >= 2;
-  const bool i_send = a.mode == 0 || a.mode == 2 || (a.mode == 3 && r == a.root);
+  const bool collective = mode >= 2;
+  const bool i_send = mode == 0 || mode == 2 || (mode == 3 && r == a.root);
   const size_t area = CCB_DATA_OFFSET + (size_t)(a.c.epoch & 1u) * a.c.half_bytes;
   if (threadIdx.x == 0) {
     sync.fail = 0;
@@ -373,11 +383,20 @@ __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  unsigned long long produced = 0;
+  uint32_t phases = 0u;     // bit s: parity the next wait on mbarrier s expects
+  auto landed = [&](int slot) {   // bounded wait for the copy into buffer `slot`; reports a copy that never came
+    const bool ok = mbar_wait(&mbar[slot], (phases >> slot) & 1u);
+    phases ^= 1u << slot;
+    if (!ok) {
+      if (threadIdx.x == 0 && a.c.status) atomicOr(a.c.status + CCB_STATUS_FLAGS, CCB_ST_TIMEOUT);
+      sync.fail = 1;
+    }
+  };
 
   // ------------------------------------------------------------- compress ----
-  if (i_send && a.mode != 1) {
+  if (i_send && mode != 1) {
     const float* in = a.f[lr].in;
+    unsigned long long produced = 0;
     // one thread starts the copy of this CTA's tile of group g into landing buffer `slot`
     auto prefetch = [&](unsigned int g, int slot) {
       const unsigned int tile = g * kClusterSize + k;
@@ -388,80 +407,95 @@ __global__ void __launch_bounds__(kSzThreads) sz_kernel(const __grid_constant__ 
       mbar_expect_tx(&mbar[slot], kTileVals * 4);
       tma_load_3d(vals2[slot], &a.tmap[lr], t.x0, t.y0, t.z0, &mbar[slot]);
     };
-    prefetch(cl, 0);
-    uint32_t it = 0;
-    for (unsigned int g = cl; g < a.ngroups; g += ncl, ++it) {
-      const int slot = it & 1;
-      const unsigned int tile = g * kClusterSize + k;
-      uint32_t size = 0;
-      prefetch(g + ncl, slot ^ 1);   // that buffer was released by the __syncthreads ending the previous pack
-      if (tile < ntiles) {
-        const TileCoord t = tile_coord(a, tile);
-        float* cur = vals2[slot];
-        if (a.use_tma) {
-          if (!mbar_wait(&mbar[slot], (it >> 1) & 1u)) {  // the copy never landed: report and leave
-            if (threadIdx.x == 0 && a.c.status) atomicOr(a.c.status + CCB_STATUS_FLAGS, CCB_ST_TIMEOUT);
-            sync.fail = 1;
-          }
-        } else {
-          load_tile_plain(in, cur, t, a);
-        }
-        __syncthreads();
-        size = sync.fail ? 0 : pack_tile(cur, pk, s_scan, a);
-      }
-      if (threadIdx.x == 0) s_size[slot] = size;
-      // One cluster barrier per group: the sizes of group parity `slot` are rewritten only
-      // two groups later, after every CTA has passed the next barrier, by which time all
-      // reads of this group's sizes are done.
-      cluster.sync();
-      uint32_t off = 0;
-      for (int j = 0; j < k; ++j) off += *cluster.map_shared_rank(&s_size[slot], j);
-      // copy the packed tile out: to the local buffer, or to every destination's arena
-      auto emit = [&](char* slot_base) {
+    // copies a packed tile out: to the local buffer, or to every destination's arena
+    auto emit = [&](unsigned int g, uint32_t off, uint32_t size, const unsigned char* pk) {
+      auto to = [&](char* slot_base) {
         char* grp = slot_base + (size_t)g * kGroupStride;
         if (threadIdx.x == 0) reinterpret_cast<uint32_t*>(grp)[k] = size;
         char* dst = grp + kGroupHeader + off;
         const uint4* s4 = reinterpret_cast<const uint4*>(pk);
         for (uint32_t i = threadIdx.x; i < size / 16; i += kSzThreads) stg(dst + 16 * i, s4[i]);
       };
-      if (a.mode == 0) {
-        emit(a.local_out);
+      if (mode == 0) {
+        to(a.local_out);
       } else {
-        for (int j = 0; j < n; ++j) emit(a.c.arena[(r + j) % n] + area + (size_t)r * a.slot_bytes);
+        for (int j = 0; j < n; ++j) to(a.c.arena[(r + j) % n] + area + (size_t)r * a.slot_bytes);
       }
+    };
+    prefetch(cl, 0);
+    uint32_t it = 0, pend_size = 0, pend_off = 0;
+    unsigned int pend_g = 0;
+    bool pend = false;
+    for (unsigned int g = cl; g < a.ngroups; g += ncl, ++it) {
+      const int slot = it & 1;
+      const unsigned int tile = g * kClusterSize + k;
+      uint32_t size = 0;
+      prefetch(g + ncl, slot ^ 1);   // that buffer was released by the __syncthreads ending the previous pack
+      if (tile < ntiles) {
+        float* cur = vals2[slot];
+        if (a.use_tma) landed(slot);
+        else load_tile_plain(in, cur, tile_coord(a, tile), a);
+        __syncthreads();
+        size = sync.fail ? 0 : pack_tile(cur, pk2[slot], s_tot, a);
+      }
+      if (threadIdx.x == 0) s_size[slot] = size;
+      // One cluster barrier per group, split in two so that the copy-out of the PREVIOUS
+      // tile runs while the cluster gathers. s_size[slot] is rewritten two groups later,
+      // after every CTA has passed the next barrier, when all reads of it are done.
+      cluster_arrive();
+      if (pend) emit(pend_g, pend_off, pend_size, pk2[slot ^ 1]);
+      cluster_wait();
+      uint32_t off = 0;
+      for (int j = 0; j < k; ++j) off += *cluster.map_shared_rank(&s_size[slot], j);
+      pend = true; pend_g = g; pend_off = off; pend_size = size;
       produced += size;
-      __syncthreads();   // pk is free again
     }
-    cluster.sync();      // nobody leaves (or moves on) while a neighbour may still read its sizes
+    if (pend) emit(pend_g, pend_off, pend_size, pk2[(it - 1) & 1]);
+    cluster.sync();      // nobody leaves while a neighbour may still read its sizes
     if (a.used_bytes && threadIdx.x == 0 && produced) atomicAdd(a.used_bytes + lr, produced + 0ull);
   }
-  if (a.mode == 0) return;
+  if (mode == 0) return;
 
   // --------------------------------------------------------------- signal ----
   if (collective) {
     __syncthreads();
     if (i_send && threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(a.c.arena[threadIdx.x], 0, r, b), a.c.epoch);
-    const uint32_t srcmask = a.mode == 2 ? 0xffu : (1u << a.root);
+    const uint32_t srcmask = mode == 2 ? 0xffu : (1u << a.root);
     if (!cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, srcmask, 0xA0)) return;
   }
 
   // ------------------------------------------------------------ decompress ---
-  const int nsrc = a.mode == 2 ? n : 1;
-  for (int si = 0; si < nsrc; ++si) {
-    const int q = a.mode == 2 ? (r + si) % n : a.root;
-    const char* slot = a.mode == 1 ? a.local_in : a.c.arena[r] + area + (size_t)q * a.slot_bytes;
-    float* out = a.f[lr].out + (a.mode == 2 ? (size_t)q * a.nx * a.ny * a.nz : 0);
-    for (unsigned int g = cl; g < a.ngroups; g += ncl) {
-      const unsigned int tile = g * kClusterSize + k;
-      if (tile >= ntiles) continue;
-      const char* grp = slot + (size_t)g * kGroupStride;
-      const int ln = threadIdx.x & 31;   // sizes of the tiles before this one, one per lane
-      const uint32_t off = __reduce_add_sync(0xffffffffu, ln < k ? ldg_cg_u32(grp + 4 * ln) : 0u);
-      unpack_tile(reinterpret_cast<const unsigned char*>(grp + kGroupHeader + off), reinterpret_cast<int*>(vals), a, out,
-                  tile_coord(a, tile));
+  // Work items (source, group) of this cluster, flattened; the size words of the next
+  // item's group are fetched while this item is decoded.
+  const int nsrc = mode == 2 ? n : 1;
+  const unsigned int per_src = cl < a.ngroups ? (a.ngroups - cl + ncl - 1) / ncl : 0;
+  const unsigned int nitems = per_src * nsrc;
+  const int ln = threadIdx.x & 31;
+  auto group_of = [&](unsigned int f) -> const char* {
+    const int q = mode == 2 ? (r + (int)(f / per_src)) % n : a.root;
+    const char* slot = mode == 1 ? a.local_in : a.c.arena[r] + area + (size_t)q * a.slot_bytes;
+    return slot + (size_t)(cl + (f % per_src) * ncl) * kGroupStride;
+  };
+  auto valid = [&](unsigned int f) { return f < nitems && (cl + (f % per_src) * ncl) * kClusterSize + k < ntiles; };
+  auto sizes_of = [&](unsigned int f) -> uint32_t {   // lane j < k gets the size of tile j of the group
+    return (valid(f) && ln < k) ? ldg_cg_u32(group_of(f) + 4 * ln) : 0u;
+  };
+  uint32_t sz_next = sizes_of(0);
+  for (unsigned int f = 0; f < nitems; ++f) {
+    const uint32_t sz = sz_next;
+    sz_next = sizes_of(f + 1);
+    if (!valid(f)) continue;
+    uint32_t off = __reduce_add_sync(0xffffffffu, sz);
+    if (off > (uint32_t)(kClusterSize * kTileCap)) {   // damaged size words: stay inside the slot and flag it
+      off = 0;
+      if (threadIdx.x == 0 && a.c.status) atomicOr(a.c.status + CCB_STATUS_FLAGS, CCB_ST_TIMEOUT);
     }
+    const int q = mode == 2 ? (r + (int)(f / per_src)) % n : a.root;
+    float* out = a.f[lr].out + (mode == 2 ? (size_t)q * a.nx * a.ny * a.nz : 0);
+    unpack_tile(reinterpret_cast<const unsigned char*>(group_of(f)) + kGroupHeader + off, reinterpret_cast<int*>(vals2[0]), a,
+                out, tile_coord(a, (cl + (f % per_src) * ncl) * kClusterSize + k));
   }
-  if (a.mode == 3) end_handshake(sync, a.c, r);
+  if (mode == 3) end_handshake(sync, a.c, r);
 }
 
 // --------------------------------------------------------------------- host --
@@ -506,6 +540,7 @@ static void fill_geometry(SzArgs& a, int nx, int ny, int nz, float eb) {
 
 // Launch with a cluster of 8 CTAs; cooperative when the kernel waits on peers.
 static int sz_launch(SzArgs& a, int nlocal, int num_sms, bool waits, cudaStream_t stream) {
+  void (*kernel)(const SzArgs) = a.mode == 0 ? sz_kernel<0> : a.mode == 1 ? sz_kernel<1> : sz_kernel<2>;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cudaLaunchAttribute attrs[2];
@@ -520,7 +555,7 @@ static int sz_launch(SzArgs& a, int nlocal, int num_sms, bool waits, cudaStream_
   cfg.numAttrs = 1;
   cfg.gridDim = dim3(kClusterSize, 1, 1);
   int max_clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&max_clusters, sz_kernel, &cfg) != cudaSuccess || max_clusters < 1) {
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg) != cudaSuccess || max_clusters < 1) {
     (void)cudaGetLastError();
     max_clusters = num_sms / kClusterSize;
   }
@@ -535,11 +570,11 @@ static int sz_launch(SzArgs& a, int nlocal, int num_sms, bool waits, cudaStream_
     attrs[1].val.cooperative = 1;
     cfg.numAttrs = 2;
   }
-  cudaError_t e = cudaLaunchKernelEx(&cfg, sz_kernel, a);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
   if (e != cudaSuccess && waits) {  // some drivers refuse cluster + cooperative: the bounded grid still fits
     (void)cudaGetLastError();
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, sz_kernel, a);
+    e = cudaLaunchKernelEx(&cfg, kernel, a);
   }
   if (e != cudaSuccess) {
     set_error("sz kernel launch failed: %s", cudaGetErrorString(e));
