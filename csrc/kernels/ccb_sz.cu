@@ -460,8 +460,9 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
   if (collective) {
     __syncthreads();
     if (i_send && threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(a.c.arena[threadIdx.x], 0, r, b), a.c.epoch);
-    const uint32_t srcmask = mode == 2 ? 0xffu : (1u << a.root);
-    if (!cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, srcmask, 0xA0)) return;
+    // Broadcast waits for the root here. All-gather waits source by source inside the
+    // decode loop, own field first, so decoding overlaps the arrival of the later ones.
+    if (mode == 3 && !cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, 1u << a.root, 0xA0)) return;
   }
 
   // ------------------------------------------------------------ decompress ---
@@ -482,8 +483,13 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
   };
   uint32_t sz_next = sizes_of(0);
   for (unsigned int f = 0; f < nitems; ++f) {
+    if (mode == 2 && f % per_src == 0) {   // first item of the next source: its CTA of the same index must be done
+      const int src = (r + (int)(f / per_src)) % n;
+      if (src != r && !cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, 1u << src, 0xA0)) return;
+      sz_next = sizes_of(f);               // (re)read now that the source's bytes are visible
+    }
     const uint32_t sz = sz_next;
-    sz_next = sizes_of(f + 1);
+    sz_next = (mode == 2 && (f + 1) % per_src == 0) ? 0u : sizes_of(f + 1);
     if (!valid(f)) continue;
     uint32_t off = __reduce_add_sync(0xffffffffu, sz);
     if (off > (uint32_t)(kClusterSize * kTileCap)) {   // damaged size words: stay inside the slot and flag it

@@ -116,6 +116,69 @@ def _body(comm, rank, world, dev):
         ex = sum(t.double() for t in xs).float()
         assert torch.allclose(red.cpu(), ex, rtol=1e-5, atol=1e-5)
     assert comm.status()[0] == 0
+    _sz_and_moe(comm, rank, world, dev, gather_inputs)
+
+
+def _sz_and_moe(comm, rank, world, dev, gather_inputs):
+    """Error-bounded AllGather / Broadcast and MoE dispatch + combine over real peers."""
+    from ccbench_b200.models.workloads import moe_routing, smooth_field
+    from ccbench_b200.ops import sz
+    from ccbench_b200.parallel import moe
+
+    n = 96
+    fld = smooth_field(n, seed=rank, device=dev)
+    flds = gather_inputs(fld)
+    eb = 1e-3 * max((f.max() - f.min()).item() for f in flds)
+    eb32 = float(torch.tensor(eb, dtype=torch.float32))
+    recv = torch.zeros((world, n, n, n), device=dev)
+    for _ in range(3):
+        sz.all_gather(comm, fld, recv, eb)
+    torch.cuda.synchronize()
+    assert comm.status()[0] == 0
+    for q in range(world):
+        assert (recv[q].cpu() - flds[q]).abs().max().item() <= eb32, ("sz all_gather bound", q)
+        buf, _ = sz.compress(flds[q].to(dev), eb)
+        assert torch.equal(recv[q], sz.decompress(buf, fld.shape, eb)), ("sz all_gather vs local codec", q)
+    out = torch.zeros_like(fld)
+    for root in (0, world - 1):
+        for _ in range(2):
+            sz.broadcast(comm, fld, out, eb, root=root)
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0
+        assert (out.cpu() - flds[root]).abs().max().item() <= eb32, ("sz broadcast bound", root)
+
+    T, H, dt = 300, 1024, torch.bfloat16
+    x = torch.randn(T, H, generator=torch.Generator().manual_seed(rank)).to(dt).to(dev)
+    ids, gates = moe_routing(T, world, 2, seed=rank)
+    rt = moe.plan_route(ids, gates, world)
+    counts = [None] * world
+    dist.all_gather_object(counts, rt.send_counts.tolist())
+    route = moe.Route(rt.perm.to(dev), rt.dest_rank.to(dev), rt.pos.to(dev), rt.gate.to(dev), rt.send_counts, rt.topk)
+    rows_in = sum(counts[s][rank] for s in range(world))
+    for codec in ("fp8", "none"):
+        recv = torch.zeros(max(rows_in, 1), H, dtype=dt, device=dev)
+        for _ in range(2):
+            moe.dispatch(comm, x, recv, route, counts, codec=codec)
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0
+        xs = gather_inputs(x)
+        perms = [None] * world
+        dist.all_gather_object(perms, rt.perm.tolist())
+        want = []
+        for s in range(world):
+            start = sum(counts[s][:rank])
+            rows = torch.tensor(perms[s][start:start + counts[s][rank]], dtype=torch.long)
+            want.append(C.roundtrip(xs[s][rows].float(), codec, dt).to(dt).reshape(-1, H))
+        want = torch.cat(want)
+        assert torch.equal(recv[:rows_in].cpu(), want), ("moe dispatch", codec)
+        # identity experts: combine returns every token gate-weighted (gates sum to 1)
+        out = torch.zeros(T, H, dtype=dt, device=dev)
+        moe.combine(comm, recv, out, route, counts, codec=codec)
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0
+        tol = {"fp8": 0.15, "none": 0.02}[codec]
+        rel = ((out.float() - x.float()).norm() / x.float().norm()).item()
+        assert rel < tol, ("moe combine", codec, rel)
 
 
 if __name__ == "__main__":
