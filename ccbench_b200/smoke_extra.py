@@ -1,5 +1,64 @@
-"""Extra one-step checks run by smoke(); grows with the kernel families."""
+"""Extra one-step checks run by smoke(): one launch of every other kernel family on
+cuda:0, each compared with a plain PyTorch statement of the same operation."""
+import torch
 
 
 def run() -> None:
-    pass
+    from . import Communicator
+    from .models.workloads import moe_routing, smooth_field
+    from .ops import codecs as C
+    from .ops import sz
+    from .parallel import moe
+
+    dev = torch.device("cuda", 0)
+    n = 4
+    comm = Communicator.local(n, arena_bytes=48 << 20)
+    try:
+        # exchange family: all-gather with fp8 lanes, all-to-all verbatim
+        per = 4096 + 3
+        xs = [torch.randn(per * n, generator=torch.Generator().manual_seed(r)) for r in range(n)]
+        xg = [x.to(dev) for x in xs]
+        ag = [torch.empty(per * n * n, device=dev) for _ in range(n)]
+        comm.all_gather(xg, ag, codec="fp8")
+        a2a = [torch.empty(per * n, device=dev) for _ in range(n)]
+        comm.all_to_all(xg, a2a, codec="none")
+        torch.cuda.synchronize()
+        assert torch.equal(ag[1].cpu(), torch.cat([C.roundtrip(x, "fp8") for x in xs]))
+        assert torch.equal(a2a[2].cpu(), torch.cat([x[2 * per:3 * per] for x in xs]))
+
+        # reduce-scatter with int8 lanes
+        rs = [torch.empty(per, device=dev) for _ in range(n)]
+        comm.reduce_scatter(xg, rs, codec="int8")
+        torch.cuda.synchronize()
+        exact = sum(x[per:2 * per].double() for x in xs).float()
+        assert ((rs[1].cpu() - exact).norm() / exact.norm()).item() < 0.03
+
+        # error-bounded codec: local round trip and the fused all-gather
+        f = [smooth_field(40, seed=r, device=dev) for r in range(n)]
+        eb = 1e-3 * (f[0].max() - f[0].min()).item()
+        buf, used = sz.compress(f[0], eb)
+        back = sz.decompress(buf, f[0].shape, eb)
+        eb32 = float(torch.tensor(eb, dtype=torch.float32))
+        assert (back - f[0]).abs().max().item() <= eb32 and 0 < int(used.item()) < f[0].numel() * 4
+        recv = [torch.empty((n,) + tuple(f[0].shape), device=dev) for _ in range(n)]
+        sz.all_gather(comm, f, recv, eb)
+        torch.cuda.synchronize()
+        assert torch.equal(recv[3][0], back)
+        assert max((recv[1][q] - f[q]).abs().max().item() for q in range(n)) <= eb32
+
+        # MoE dispatch with fp8 rows, then combine with identity experts
+        T, H, dt = 128, 1024, torch.bfloat16
+        tok = [torch.randn(T, H, generator=torch.Generator().manual_seed(10 + r)).to(dt).to(dev) for r in range(n)]
+        routes = [moe.plan_route(*moe_routing(T, n, 2, seed=r, device=dev), n) for r in range(n)]
+        cm = [rt.send_counts.tolist() for rt in routes]
+        rows = [max(sum(cm[s][d] for s in range(n)), 1) for d in range(n)]
+        got = [torch.zeros(rows[d], H, dtype=dt, device=dev) for d in range(n)]
+        moe.dispatch(comm, tok, got, routes, cm, codec="fp8")
+        out = [torch.zeros(T, H, dtype=dt, device=dev) for _ in range(n)]
+        moe.combine(comm, got, out, routes, cm, codec="fp8")
+        torch.cuda.synchronize()
+        rel = ((out[0].float() - tok[0].float()).norm() / tok[0].float().norm()).item()
+        assert rel < 0.15, rel
+        assert comm.status()[0] == 0
+    finally:
+        comm.close()
