@@ -4,6 +4,7 @@ the CPU path of the 2-rank gloo benchmark; nothing here is on a GPU hot path.
 
 Codec definitions (identical to csrc/kernels/ccb_codec.cuh):
   int8  : per group of G values, scale = absmax/127, q = rint(x * (127/absmax))
+  int4  : per group of 128 values, scale = absmax/7, q = rint(x * (7/absmax)), two per byte
   fp8   : per 32 values, scale 2^e with e the smallest integer such that
           absmax * 2^-e <= 448; q = e4m3(x * 2^-e) (round to nearest even)
 The reference's int8 codec stores the reciprocal 127/absmax instead
@@ -38,6 +39,16 @@ def int8_encode(x: torch.Tensor, group: int = 128):
 
 def int8_decode(q: torch.Tensor, scale: torch.Tensor, group: int = 128) -> torch.Tensor:
     return (q.reshape(-1, group).float() * scale.reshape(-1, 1)).reshape(-1)
+
+
+def int4_roundtrip(x: torch.Tensor, group: int = 128) -> torch.Tensor:
+    """Symmetric 4-bit integers (-7..7), fp32 scale = absmax / 7 per group."""
+    xf = _pad_to(x.float(), group).reshape(-1, group)
+    m = xf.abs().amax(dim=1, keepdim=True)
+    c7 = torch.full_like(m, 7.0)
+    inv = torch.where(m > 0, c7 / m.clamp_min(torch.finfo(torch.float32).tiny), torch.zeros_like(m))
+    q = torch.round(xf * inv).clamp_(-7, 7)
+    return (q * (m / c7)).reshape(-1)[: x.numel()].reshape(x.shape)
 
 
 def int8_roundtrip(x: torch.Tensor, group: int = 128) -> torch.Tensor:
@@ -89,6 +100,8 @@ def roundtrip(x: torch.Tensor, codec: str, dtype: torch.dtype = torch.float32) -
         return int8_roundtrip(x, 256)
     if codec == "fp8":
         return fp8_roundtrip(x)
+    if codec == "int4":
+        return int4_roundtrip(x)
     if codec == "none":
         return x.float().to(dtype).float()
     raise ValueError(codec)
@@ -97,7 +110,7 @@ def roundtrip(x: torch.Tensor, codec: str, dtype: torch.dtype = torch.float32) -
 def wire_ratio(codec: str, dtype: torch.dtype) -> float:
     """Raw bytes / wire bytes of one message."""
     es = torch.empty((), dtype=dtype).element_size()
-    per = {"none": es, "int8": 1 + 4 / 128, "int8_g256": 1 + 4 / 256, "fp8": 1 + 1 / 32}[codec]
+    per = {"none": es, "int8": 1 + 4 / 128, "int8_g256": 1 + 4 / 256, "fp8": 1 + 1 / 32, "int4": 0.5 + 4 / 128}[codec]
     return es / per
 
 

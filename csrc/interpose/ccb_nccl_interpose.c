@@ -75,6 +75,7 @@ static int codec_by_name(const char *s, int dflt) {
     if (!s || !*s) return dflt;
     if (!strcasecmp(s, "int8")) return CCB_CODEC_INT8;
     if (!strcasecmp(s, "fp8")) return CCB_CODEC_FP8;
+    if (!strcasecmp(s, "int4")) return CCB_CODEC_INT4;
     if (!strcasecmp(s, "none")) return CCB_CODEC_NONE;
     if (!strcasecmp(s, "int8_g256")) return CCB_CODEC_INT8_G256;
     return dflt;

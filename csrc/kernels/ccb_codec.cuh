@@ -9,6 +9,7 @@
 //   CodecNone<T>   elements travel as T (exact for T, used for the uncompressed paths)
 //   CodecInt8<G>   int8, fp32 scale = absmax/127 per G values (G = 128 or 256)
 //   CodecFp8       fp8 e4m3, ue8m0 (power-of-two) scale byte per 32 values
+//   CodecInt4      int4, fp32 scale = absmax/7 per 128 values
 //
 // The reference's only GPU codec is int8 with a per-group reciprocal scale
 // (userconfig/wrapper_code_examples/communication/plain_nccl_compress/
@@ -122,6 +123,42 @@ struct CodecInt8 {
   static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
     pk.q = ldg_cg(slot + idx);
     pk.scale = __uint_as_float(ldg_cg_u32(slot + pad + (idx / G) * 4));
+  }
+};
+
+// Symmetric 4-bit integers, fp32 scale = absmax/7 per 128 values: 0.53 bytes per value,
+// a quarter of bf16. The reference reaches 4 bits only through the SDP4Bit-style
+// compression wrapper (userconfig/wrapper_code_examples/compression/sdp4bit/
+// sdp4bit.cu:38-51); its NCCL wrapper accepts NCCL_COMPRESS_BITS=4 but implements 8.
+struct CodecInt4 {
+  static constexpr int kId = CCB_CODEC_INT4;
+  static constexpr int kGroup = 128;
+  static constexpr int kLanes = kGroup / 16;
+  struct Packet { uint2 q; float scale; };
+  static __host__ __device__ size_t slot_bytes(size_t pad) { return pad / 2 + pad / kGroup * 4; }
+  static __device__ __forceinline__ void encode(const float (&v)[16], Packet& pk) {
+    float m = absmax16(v);
+#pragma unroll
+    for (int d = 1; d < kLanes; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    const float inv = m > 0.f ? 7.f / m : 0.f;
+    pk.scale = m / 7.f;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) w[i >> 3] |= ((uint32_t)__float2int_rn(v[i] * inv) & 0xfu) << (4 * (i & 7));
+    pk.q = make_uint2(w[0], w[1]);
+  }
+  static __device__ __forceinline__ void decode(const Packet& pk, float (&v)[16]) {
+    const uint32_t w[2] = {pk.q.x, pk.q.y};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = (float)((int)(w[i >> 3] << (28 - 4 * (i & 7))) >> 28) * pk.scale;
+  }
+  static __device__ __forceinline__ void store(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    stg8(slot + idx / 2, pk.q);
+    if ((threadIdx.x & (kLanes - 1)) == 0) reinterpret_cast<float*>(slot + pad / 2)[idx / kGroup] = pk.scale;
+  }
+  static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
+    pk.q = ldg_cg8(slot + idx / 2);
+    pk.scale = __uint_as_float(ldg_cg_u32(slot + pad / 2 + (idx / kGroup) * 4));
   }
 };
 

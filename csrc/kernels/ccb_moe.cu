@@ -136,6 +136,7 @@ static const void* moe_fn(int dtype, int codec) {
     case CCB_CODEC_INT8: return reinterpret_cast<const void*>(&moe_kernel<T, CodecInt8<128>>);        \
     case CCB_CODEC_INT8_G256: return reinterpret_cast<const void*>(&moe_kernel<T, CodecInt8<256>>);   \
     case CCB_CODEC_FP8: return reinterpret_cast<const void*>(&moe_kernel<T, CodecFp8>);               \
+    case CCB_CODEC_INT4: return reinterpret_cast<const void*>(&moe_kernel<T, CodecInt4>);             \
     default: return nullptr;                                                                          \
   }
   switch (dtype) {

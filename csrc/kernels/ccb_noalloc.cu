@@ -68,6 +68,7 @@ static const void* twoshot_fn(int dtype, int codec) {
     case CCB_CODEC_INT8: return reinterpret_cast<const void*>(&reduce_kernel<T, CodecInt8<128>, kTwoShot>);     \
     case CCB_CODEC_INT8_G256: return reinterpret_cast<const void*>(&reduce_kernel<T, CodecInt8<256>, kTwoShot>); \
     case CCB_CODEC_FP8: return reinterpret_cast<const void*>(&reduce_kernel<T, CodecFp8, kTwoShot>);            \
+    case CCB_CODEC_INT4: return reinterpret_cast<const void*>(&reduce_kernel<T, CodecInt4, kTwoShot>);          \
     default: return nullptr;                                                                                    \
   }
   switch (dtype) {

@@ -132,6 +132,7 @@ static int encode_t(int codec, const void* in, size_t count, void* wire, size_t 
     case CCB_CODEC_INT8: encode_kernel<T, CodecInt8<128>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
     case CCB_CODEC_INT8_G256: encode_kernel<T, CodecInt8<256>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
     case CCB_CODEC_FP8: encode_kernel<T, CodecFp8><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
+    case CCB_CODEC_INT4: encode_kernel<T, CodecInt4><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
     default: return CCB_ERR_UNSUPPORTED;
   }
   return CCB_OK;
@@ -144,6 +145,7 @@ static int decode_t(int codec, const void* wire, size_t count, void* out, size_t
     case CCB_CODEC_INT8: decode_kernel<T, CodecInt8<128>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
     case CCB_CODEC_INT8_G256: decode_kernel<T, CodecInt8<256>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
     case CCB_CODEC_FP8: decode_kernel<T, CodecFp8, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
+    case CCB_CODEC_INT4: decode_kernel<T, CodecInt4, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
     default: return CCB_ERR_UNSUPPORTED;
   }
   return CCB_OK;
@@ -211,6 +213,7 @@ extern "C" int ccb_reduce_recode(int codec, const void* const* wires, int nwires
     case CCB_CODEC_INT8: reduce_recode_kernel<CodecInt8<128>><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
     case CCB_CODEC_INT8_G256: reduce_recode_kernel<CodecInt8<256>><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
     case CCB_CODEC_FP8: reduce_recode_kernel<CodecFp8><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
+    case CCB_CODEC_INT4: reduce_recode_kernel<CodecInt4><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
     case CCB_CODEC_NONE: reduce_recode_kernel<CodecNone<float>><<<g, kSaThreads, 0, s>>>(wl, count, (char*)wire_out, pad); break;
     default: return CCB_ERR_UNSUPPORTED;
   }

@@ -249,6 +249,7 @@ size_t codec_slot_bytes(int codec, int dtype, size_t pad) {
     case CCB_CODEC_INT8: b = pad + pad / 128 * 4; break;
     case CCB_CODEC_INT8_G256: b = pad + pad / 256 * 4; break;
     case CCB_CODEC_FP8: b = pad + pad / 32; break;
+    case CCB_CODEC_INT4: b = pad / 2 + pad / 128 * 4; break;
     default: b = pad * elem_size(dtype); break;
   }
   return round_up(b, 256);
@@ -611,6 +612,7 @@ namespace ccb {
     case CCB_CODEC_INT8: { using TT = T; using CC = CodecInt8<128>; return EXPR; }    \
     case CCB_CODEC_INT8_G256: { using TT = T; using CC = CodecInt8<256>; return EXPR; } \
     case CCB_CODEC_FP8: { using TT = T; using CC = CodecFp8; return EXPR; }           \
+    case CCB_CODEC_INT4: { using TT = T; using CC = CodecInt4; return EXPR; }         \
     default: return nullptr;                                                         \
   }
 

@@ -7,7 +7,7 @@
  * `*compChunkBytes` bytes so that the transport needs no size exchange. The
  * reference's template decompresses to temporaries and adds with separate kernels
  * (:161-176, 212-247); here decode+add and decode+add+re-encode are single kernels.
- * Codec: $CCB_HOOK_CODEC = int8 (default) | fp8 | int8_g256 | none. */
+ * Codec: $CCB_HOOK_CODEC = int8 (default) | fp8 | int8_g256 | int4 | none. */
 #include <cuda_runtime.h>
 #include <nccl.h>
 #include <stdint.h>
@@ -26,6 +26,7 @@ static int hook_codec(void) {
     const char *e = getenv("CCB_HOOK_CODEC");
     if (!e || !strcasecmp(e, "int8")) return CCB_CODEC_INT8;
     if (!strcasecmp(e, "fp8")) return CCB_CODEC_FP8;
+    if (!strcasecmp(e, "int4")) return CCB_CODEC_INT4;
     if (!strcasecmp(e, "int8_g256")) return CCB_CODEC_INT8_G256;
     return CCB_CODEC_NONE;
 }

@@ -37,7 +37,8 @@ enum {
   CCB_CODEC_NONE = 0,     /* elements travel in their own type              */
   CCB_CODEC_INT8 = 1,     /* int8, one fp32 absmax/127 scale per 128 values */
   CCB_CODEC_FP8 = 2,      /* e4m3, one ue8m0 scale byte per 32 values       */
-  CCB_CODEC_INT8_G256 = 3 /* int8, group 256 (the reference wrapper default) */
+  CCB_CODEC_INT8_G256 = 3, /* int8, group 256 (the reference wrapper default) */
+  CCB_CODEC_INT4 = 4      /* int4, fp32 scale = absmax/7 per 128 values       */
 };
 enum { CCB_OP_SUM = 0, CCB_OP_PROD = 1, CCB_OP_MAX = 2, CCB_OP_MIN = 3 };
 /* AllReduce algorithms. */
