@@ -89,8 +89,13 @@ def main():
 
     # Warm up for at least W steps AND about a second, so that the clock sampler (one
     # nvidia-smi sample per 100 ms) sees the GPU under the same load as the timed steps.
-    sampler = ClockSampler(local_rank, 100)
-    sampler.__enter__()
+    # Rank 0 samples every GPU of the job with one nvidia-smi process and waits for its
+    # first line before any rank goes on.
+    sampler = ClockSampler(list(range(world)) if rank == 0 else 0, 100)
+    if rank == 0:
+        sampler.__enter__()
+        sampler.wait_first()
+    barrier()
     t_w = time.perf_counter()
     for _ in range(max(args.warmup, 3)):
         step()
@@ -128,7 +133,7 @@ def main():
     clocks = clk.summary()
 
     # ---- accuracy of the last result against the exact fp32 sum ----------------
-    exact = x.float()
+    exact = x.float().clone()
     if world > 1:
         dist.all_reduce(exact)
     rel_l2 = ((y.float() - exact).norm() / exact.norm()).item()

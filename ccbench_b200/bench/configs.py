@@ -53,7 +53,7 @@ def config3(comm, rank, world, dev, args):
     count = args.bytes // 2
     x = gradient_like(count, dtype, seed=rank, device=dev)
     y = torch.empty_like(x)
-    exact = x.float()
+    exact = x.float().clone()
     if world > 1:
         dist.all_reduce(exact)
     f = 2 * (world - 1) / world if world > 1 else 1.0
@@ -169,32 +169,43 @@ def config5(comm, rank, world, dev, args):
         for _ in range(nb):
             comm.reduce_scatter(g, shard, codec="int8")
 
+    def nccl_only():
+        for _ in range(nb):
+            dist.reduce_scatter_tensor(shard, g)
+
     def compute_only():
         for _ in range(nb):
             torch.matmul(a, a)
 
-    def both():
+    def both(comm_fn):
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            for _ in range(nb):
-                comm.reduce_scatter(g, shard, codec="int8")
-        for _ in range(nb):
-            torch.matmul(a, a)
+            comm_fn()
+        compute_only()
         torch.cuda.current_stream().wait_stream(side)
 
-    t_comm = _timed(comm_only, 3, 1, world, dev)
     t_comp = _timed(compute_only, 3, 1, world, dev)
-    t_both = _timed(both, 3, 1, world, dev)
-    assert comm.status()[0] == 0
-    row = {"config": 5, "op": "reduce_scatter buckets", "codec": "int8", "n": world, "buckets": nb, "bucket_bytes": bucket * 2,
-           "comm_alone_us": round(t_comm, 1), "compute_alone_us": round(t_comp, 1), "overlapped_us": round(t_both, 1),
-           "busbw_GBs": round(bucket * 2 * nb / t_comm / 1e3 * fa, 2),
-           "overlap_efficiency": round((t_comm + t_comp - t_both) / min(t_comm, t_comp), 3)}
+    # The collective kernel is one co-resident grid: with every SM taken it starves the GEMMs
+    # it should hide behind, so the grid is capped and the cap swept (0 = no cap).
+    for cap in (0, 64, 32, 16):
+        comm.set_max_ctas(cap)
+        t_comm = _timed(comm_only, 3, 1, world, dev)
+        t_both = _timed(lambda: both(comm_only), 3, 1, world, dev)
+        assert comm.status()[0] == 0
+        _emit(rank, {"config": 5, "op": "reduce_scatter buckets", "codec": "int8", "n": world, "buckets": nb, "bucket_bytes": bucket * 2,
+                     "max_ctas": cap, "comm_alone_us": round(t_comm, 1), "compute_alone_us": round(t_comp, 1),
+                     "overlapped_us": round(t_both, 1), "busbw_GBs": round(bucket * 2 * nb / t_comm / 1e3 * fa, 2),
+                     "exposed_comm_us": round(t_both - t_comp, 1),
+                     "overlap_efficiency": round((t_comm + t_comp - t_both) / min(t_comm, t_comp), 3)})
+    comm.set_max_ctas(0)
     if world > 1:
-        t_nccl = _timed(lambda: [dist.reduce_scatter_tensor(shard, g) for _ in range(nb)], 3, 1, world, dev)
-        row["nccl_comm_alone_us"] = round(t_nccl, 1)
-        row["nccl_busbw_GBs"] = round(bucket * 2 * nb / t_nccl / 1e3 * fa, 2)
-    _emit(rank, row)
+        t_nccl = _timed(nccl_only, 3, 1, world, dev)
+        t_both = _timed(lambda: both(nccl_only), 3, 1, world, dev)
+        _emit(rank, {"config": 5, "op": "reduce_scatter buckets", "codec": "none (nccl)", "n": world, "buckets": nb,
+                     "bucket_bytes": bucket * 2, "comm_alone_us": round(t_nccl, 1), "compute_alone_us": round(t_comp, 1),
+                     "overlapped_us": round(t_both, 1), "busbw_GBs": round(bucket * 2 * nb / t_nccl / 1e3 * fa, 2),
+                     "exposed_comm_us": round(t_both - t_comp, 1),
+                     "overlap_efficiency": round((t_nccl + t_comp - t_both) / min(t_nccl, t_comp), 3)})
 
 
 def main(argv=None):

@@ -2,7 +2,7 @@
 (torch.distributed) timed the same way as the uncompressed baseline.
 
     python -m torch.distributed.run --nproc-per-node N -m ccbench_b200.bench.sweep \
-        --min 8 --max 1073741824 --dtype bf16 --variants none:auto,int8:twoshot,nccl
+        --min-bytes 8 --max-bytes 1073741824 --dtype bf16 --variants none:auto,int8:twoshot,nccl
 
 Every number is CUDA-event time on the device, maximum over ranks, after warm-up.
 Columns follow the result CSV layout of this repository
@@ -58,8 +58,10 @@ def timed(fn, iters, warmup, world, dev, flush=None):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("--min", type=int, default=8)
-    ap.add_argument("--max", type=int, default=1 << 30)
+    # the long names are the ones to use under torch.distributed.run, whose own parser
+    # takes a bare --max for an abbreviation of --max-restarts
+    ap.add_argument("--min", "--min-bytes", dest="min", type=int, default=8)
+    ap.add_argument("--max", "--max-bytes", dest="max", type=int, default=1 << 30)
     ap.add_argument("--factor", type=int, default=2)
     ap.add_argument("--sizes", default="", help="comma-separated byte sizes (overrides min/max)")
     ap.add_argument("--dtype", default="bf16")
@@ -103,7 +105,7 @@ def main(argv=None):
         gen = gradient_like if args.data == "grad" else uniform_pm1
         x = gen(count, dtype, seed=rank, device=dev)
         y = torch.empty_like(x)
-        exact = x.float()
+        exact = x.float().clone()
         if world > 1:
             dist.all_reduce(exact)
         for var in args.variants.split(","):

@@ -13,7 +13,10 @@ _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,
 
 
 class ClockSampler:
-    def __init__(self, gpu_index: int = 0, period_ms: int = 100):
+    def __init__(self, gpu_index=0, period_ms: int = 100):
+        """gpu_index: one index, or a list of indices sampled together by one process."""
+        if isinstance(gpu_index, (list, tuple)):
+            gpu_index = ",".join(str(i) for i in gpu_index)
         self.gpu_index, self.period_ms = gpu_index, period_ms
         self.proc = None
         self.file = None
@@ -26,6 +29,24 @@ class ClockSampler:
                 [exe, f"--query-gpu={_QUERY}", "--format=csv,noheader,nounits", "-i", str(self.gpu_index),
                  "-lms", str(self.period_ms)], stdout=self.file, stderr=subprocess.DEVNULL)
         return self
+
+    def wait_first(self, timeout_s: float = 15.0) -> bool:
+        """Blocks until the first sample is in the file: nvidia-smi takes a second or
+        more to start on a host with many GPUs, and a timed region that ends before
+        that would have no clock record."""
+        import os
+        import time
+
+        if not self.file:
+            return False
+        t0 = time.time()
+        while time.time() - t0 < timeout_s:
+            if os.path.getsize(self.file.name) > 0:
+                return True
+            if self.proc.poll() is not None:
+                return False
+            time.sleep(0.05)
+        return False
 
     def __exit__(self, *exc):
         if self.proc:

@@ -29,6 +29,10 @@ constexpr int kTileElems = kWarpElems * kWarps;  // 8192
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -56,9 +60,18 @@ __device__ __forceinline__ uint32_t* ctrl_ptr(char* arena, int word) {
 
 // Publish "everything this CTA stored before the preceding __syncthreads() is
 // visible" to the owner of `flag`. Called by ONE thread after a __syncthreads().
+// One system-scope fence followed by a relaxed store is a release pattern; a fence
+// costs a round trip to every peer with stores in flight, so there is exactly one.
 __device__ __forceinline__ void signal_flag(uint32_t* flag, uint32_t epoch) {
-  __threadfence_system();
-  st_release_sys(flag, epoch);
+  fence_acq_rel_sys();
+  st_relaxed_sys(flag, epoch);
+}
+// The same towards several peers at once: ONE fence, then flag (slot, src, cta) in the
+// arena of every rank in `mask`. Called by ONE thread after a __syncthreads().
+__device__ __forceinline__ void signal_peers(const CommDev& c, uint32_t mask, int slot, int src, int cta) {
+  fence_acq_rel_sys();
+  for (int p = 0; p < c.nranks; ++p)
+    if ((mask >> p) & 1u) st_relaxed_sys(flag_ptr(c.arena[p], slot, src, cta), c.epoch);
 }
 
 // Bounded wait: returns true when *flag has reached `epoch` (wrap-safe compare).

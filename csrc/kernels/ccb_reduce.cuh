@@ -197,9 +197,11 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
             store16f_plain(efs, idx, valid, d);
           }
         }
-        __syncthreads();
-        if (threadIdx.x == 0) signal_flag(flag_ptr(c.arena[p], 2 * w, r, b), c.epoch);
       }
+      // one barrier and ONE fence for all destinations: a fence per destination costs a
+      // round trip each, seven in a row at eight ranks
+      __syncthreads();
+      if (threadIdx.x == 0) signal_peers(c, rooted ? ((r != a.root) ? (1u << a.root) : 0u) : (((1u << n) - 1u) & ~(1u << r)), 2 * w, r, b);
     };
 
     auto phase2 = [&](int w) -> bool {
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
       }
       if (a.mode == CCB_MODE_ALLREDUCE) {
         __syncthreads();
-        if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 2 * w + 1, r, b), c.epoch);
+        if (threadIdx.x == 0) signal_peers(c, ((1u << n) - 1u) & ~(1u << r), 2 * w + 1, r, b);
       }
       return true;
     };
