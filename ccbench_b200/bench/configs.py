@@ -162,7 +162,8 @@ def config5(comm, rank, world, dev, args):
     g = gradient_like(bucket, dt, seed=rank, device=dev)
     shard = torch.empty(bucket // world, dtype=dt, device=dev)
     nb = args.buckets
-    side = torch.cuda.Stream()
+    # high priority: the collective's CTAs take the first SMs a GEMM wave frees, instead of queueing behind it
+    side = torch.cuda.Stream(priority=-1)
     a = torch.randn(8192, 8192, device=dev, dtype=dt)
 
     def comm_only():
@@ -228,7 +229,7 @@ def main(argv=None):
         arena = 2 * world * sz.capacity((a.field,) * 3) + (64 << 20)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        comm = Communicator.from_torch_distributed(arena_bytes=arena)
+        comm = Communicator.from_torch_distributed(arena_bytes=arena, nvls=os.environ.get("CCB_NVLS", "1") == "1")
     else:
         comm = Communicator.create(0, 1, f"cfg{os.getpid()}", arena_bytes=arena)
     {3: config3, 4: config4, 5: config5}[a.config](comm, rank, world, dev, a)

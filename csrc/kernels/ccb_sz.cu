@@ -40,6 +40,7 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "../rt/ccb_rt_internal.h"
@@ -81,6 +82,7 @@ struct SzArgs {
   int mode;                          // 0 compress to local_out, 1 decompress from local_in, 2 all-gather, 3 broadcast
   int root;
   int rank0, nlocal;
+  unsigned int bcast_waves;          // progress steps a broadcast root publishes (1..kMaxBcastWaves)
   unsigned long long slot_bytes;     // arena bytes of one source's slot (ngroups * kGroupStride, rounded)
 };
 
@@ -179,7 +181,11 @@ constexpr float kRoundMagic = 12582912.f;   // 1.5 * 2^23: adding and subtractin
 
 // Packs the tile held in `vals` (fp32, [z][y][x]) into `pk`; returns its byte size.
 // The codes overwrite the values in shared memory (each thread its own eight words).
-__device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, int* s_tot, const SzArgs& a) {
+// With `recon` set, the decoder's view of the tile (q * step, or the raw values of a raw
+// tile) is also written to its place in that field: the sender's own copy of what every
+// receiver will decode, without a decode pass.
+__device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, int* s_tot, const SzArgs& a,
+                                              float* recon = nullptr, TileCoord tc = TileCoord{0, 0, 0}) {
   const int lane = threadIdx.x & 31, z = threadIdx.x >> 5;
   int4* q4 = reinterpret_cast<int4*>(vals) + 2 * threadIdx.x;
   float x[8];
@@ -204,7 +210,25 @@ __device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, in
     bad |= fabsf(__fsub_rn(x[e], __fmul_rn(rf, a.two_eb))) > a.eb;
     q[e] = (int)rf;
   }
-  if (__syncthreads_or(bad)) {  // raw tile: marker + the fp32 values
+  const bool raw_tile = __syncthreads_or(bad);
+  if (recon) {
+    const int gx = tc.x0 + 8 * (lane & 3), gy = tc.y0 + (lane >> 2), gz = tc.z0 + z;
+    if (gy < a.ny && gz < a.nz) {
+      float* row = recon + ((size_t)gz * a.ny + gy) * a.nx + gx;
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = raw_tile ? x[e] : __fmul_rn((float)q[e], a.two_eb);
+      if (gx + 8 <= a.nx && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        reinterpret_cast<float4*>(row)[0] = make_float4(o[0], o[1], o[2], o[3]);
+        reinterpret_cast<float4*>(row)[1] = make_float4(o[4], o[5], o[6], o[7]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (gx + e < a.nx) row[e] = o[e];
+      }
+    }
+  }
+  if (raw_tile) {  // raw tile: marker + the fp32 values
     for (int i = threadIdx.x; i < kRows; i += kSzThreads) pk[i] = (i == 0) ? 255 : 0;
     float* raw = reinterpret_cast<float*>(pk + kRows);
     for (int i = threadIdx.x; i < kTileVals; i += kSzThreads) raw[i] = vals[i];
@@ -348,16 +372,24 @@ __device__ __forceinline__ void load_tile_plain(const float* in, float* vals, co
     vals[(z * kTY + y) * kTX + lane] = v;
   }
 }
+__device__ __forceinline__ void multimem_st(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void multimem_st_u32(void* p, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-constexpr int kStage = kTileCap + 16;   // one packed tile, 16-byte granular
+constexpr int kStage = kTileCap + 16;
+constexpr unsigned int kMaxBcastWaves = 8;   // most progress steps of a broadcast (flag slots 0..7)   // one packed tile, 16-byte granular
 
 // kKind: 0 compress into a local buffer, 1 decompress from one, 2 the collectives (mode 2
 // all-gather, 3 broadcast). One body, three instantiations, so that each direction gets its
 // own register allocation and occupancy.
 template <int kKind>
-__global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(const __grid_constant__ SzArgs a) {
+__global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : kKind == 2 ? 5 : 4) sz_kernel(const __grid_constant__ SzArgs a) {
   const int mode = kKind == 2 ? a.mode : kKind;
+  const unsigned int kBcastWaves = a.bcast_waves;
   // Two 8 KB buffers: compress lands the next tile in one while the other is packed;
   // decompress prefixes in vals2[0].
   __shared__ __align__(128) float vals2[2][kTileVals];
@@ -393,6 +425,7 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
     }
   };
 
+  if (collective) trace_mark(a.c, 0);
   // ------------------------------------------------------------- compress ----
   if (i_send && mode != 1) {
     const float* in = a.f[lr].in;
@@ -407,21 +440,36 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
       mbar_expect_tx(&mbar[slot], kTileVals * 4);
       tma_load_3d(vals2[slot], &a.tmap[lr], t.x0, t.y0, t.z0, &mbar[slot]);
     };
-    // copies a packed tile out: to the local buffer, or to every destination's arena
+    // copies a packed tile out: to the local buffer, to every peer's arena one by one, or,
+    // where the arenas are bound to an NVLink multicast object, ONCE to the multicast
+    // address: the switch replicates it, the sender's link carries the bytes one time.
+    // The sender keeps no packed copy of its own field (pack_tile wrote the reconstruction).
+    const bool use_mc = kKind == 2 && a.c.mc_arena != nullptr && a.nlocal == 1;
     auto emit = [&](unsigned int g, uint32_t off, uint32_t size, const unsigned char* pk) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(pk);
       auto to = [&](char* slot_base) {
         char* grp = slot_base + (size_t)g * kGroupStride;
         if (threadIdx.x == 0) reinterpret_cast<uint32_t*>(grp)[k] = size;
         char* dst = grp + kGroupHeader + off;
-        const uint4* s4 = reinterpret_cast<const uint4*>(pk);
         for (uint32_t i = threadIdx.x; i < size / 16; i += kSzThreads) stg(dst + 16 * i, s4[i]);
       };
       if (mode == 0) {
         to(a.local_out);
+      } else if (use_mc) {
+        char* grp = a.c.mc_arena + area + (size_t)r * a.slot_bytes + (size_t)g * kGroupStride;
+        if (threadIdx.x == 0) multimem_st_u32(grp + 4 * k, size);
+        char* dst = grp + kGroupHeader + off;
+        for (uint32_t i = threadIdx.x; i < size / 16; i += kSzThreads) multimem_st(dst + 16 * i, s4[i]);
       } else {
-        for (int j = 0; j < n; ++j) to(a.c.arena[(r + j) % n] + area + (size_t)r * a.slot_bytes);
+        for (int j = 1; j < n; ++j) to(a.c.arena[(r + j) % n] + area + (size_t)r * a.slot_bytes);
       }
     };
+    // broadcast: the root's CTAs publish their progress in kBcastWaves steps (flag slot =
+    // wave), so that the receivers decode the first groups while the last are still packed
+    const unsigned int my_iters = cl < a.ngroups ? (a.ngroups - cl + ncl - 1) / ncl : 0;
+    auto wave_end = [&](unsigned int w) { return (unsigned int)(((unsigned long long)my_iters * (w + 1)) / kBcastWaves); };
+    unsigned int wave = 0;
+    float* own_out = kKind == 2 ? a.f[lr].out + (mode == 2 ? (size_t)r * a.nx * a.ny * a.nz : 0) : nullptr;
     prefetch(cl, 0);
     uint32_t it = 0, pend_size = 0, pend_off = 0;
     unsigned int pend_g = 0;
@@ -436,13 +484,25 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
         if (a.use_tma) landed(slot);
         else load_tile_plain(in, cur, tile_coord(a, tile), a);
         __syncthreads();
-        size = sync.fail ? 0 : pack_tile(cur, pk2[slot], s_tot, a);
+        size = sync.fail ? 0 : pack_tile(cur, pk2[slot], s_tot, a, own_out, tile_coord(a, tile));
+      } else {
+        __syncthreads();   // keeps one CTA barrier per iteration between a copy-out and its signal
       }
       if (threadIdx.x == 0) s_size[slot] = size;
       // One cluster barrier per group, split in two so that the copy-out of the PREVIOUS
       // tile runs while the cluster gathers. s_size[slot] is rewritten two groups later,
       // after every CTA has passed the next barrier, when all reads of it are done.
       cluster_arrive();
+      if (mode == 3 && it >= 1) {
+        // Tiles 0 .. it-2 were copied out one iteration ago by every thread (the barriers of
+        // the pack above order those copies before this point), so their stores have had
+        // time to complete and the fence of the signal is short.
+        while (wave < kBcastWaves && wave_end(wave) <= it - 1) {
+          if (threadIdx.x == 0 && wave_end(wave) > (wave ? wave_end(wave - 1) : 0u))
+            signal_peers(a.c, ((1u << n) - 1u) & ~(1u << r), (int)wave, r, b);
+          ++wave;
+        }
+      }
       if (pend) emit(pend_g, pend_off, pend_size, pk2[slot ^ 1]);
       cluster_wait();
       uint32_t off = 0;
@@ -451,29 +511,34 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
       produced += size;
     }
     if (pend) emit(pend_g, pend_off, pend_size, pk2[(it - 1) & 1]);
+    if (mode == 3) {     // the remaining waves (the last one always ends here)
+      __syncthreads();
+      if (threadIdx.x == 0)
+        for (; wave < kBcastWaves; ++wave)
+          if (wave_end(wave) > (wave ? wave_end(wave - 1) : 0u)) signal_peers(a.c, ((1u << n) - 1u) & ~(1u << r), (int)wave, r, b);
+    }
     cluster.sync();      // nobody leaves while a neighbour may still read its sizes
     if (a.used_bytes && threadIdx.x == 0 && produced) atomicAdd(a.used_bytes + lr, produced + 0ull);
   }
   if (mode == 0) return;
 
   // --------------------------------------------------------------- signal ----
+  if (collective) trace_mark(a.c, 1);
   if (collective) {
     __syncthreads();
-    if (i_send && threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(a.c.arena[threadIdx.x], 0, r, b), a.c.epoch);
-    // Broadcast waits for the root here. All-gather waits source by source inside the
-    // decode loop, own field first, so decoding overlaps the arrival of the later ones.
-    if (mode == 3 && !cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, 1u << a.root, 0xA0)) return;
+    if (mode == 2 && threadIdx.x == 0) signal_peers(a.c, ((1u << n) - 1u) & ~(1u << r), 0, r, b);
+    // All-gather waits source by source inside the decode loop; broadcast wave by wave.
   }
 
   // ------------------------------------------------------------ decompress ---
   // Work items (source, group) of this cluster, flattened; the size words of the next
   // item's group are fetched while this item is decoded.
-  const int nsrc = mode == 2 ? n : 1;
+  const int nsrc = mode == 2 ? n - 1 : (mode == 3 && r == a.root) ? 0 : 1;   // the sender's own copy is already written
   const unsigned int per_src = cl < a.ngroups ? (a.ngroups - cl + ncl - 1) / ncl : 0;
   const unsigned int nitems = per_src * nsrc;
   const int ln = threadIdx.x & 31;
   auto group_of = [&](unsigned int f) -> const char* {
-    const int q = mode == 2 ? (r + (int)(f / per_src)) % n : a.root;
+    const int q = mode == 2 ? (r + 1 + (int)(f / per_src)) % n : a.root;
     const char* slot = mode == 1 ? a.local_in : a.c.arena[r] + area + (size_t)q * a.slot_bytes;
     return slot + (size_t)(cl + (f % per_src) * ncl) * kGroupStride;
   };
@@ -481,26 +546,45 @@ __global__ void __launch_bounds__(kSzThreads, kKind == 1 ? 6 : 4) sz_kernel(cons
   auto sizes_of = [&](unsigned int f) -> uint32_t {   // lane j < k gets the size of tile j of the group
     return (valid(f) && ln < k) ? ldg_cg_u32(group_of(f) + 4 * ln) : 0u;
   };
-  uint32_t sz_next = sizes_of(0);
+  if (collective) trace_mark(a.c, 2);
+  auto dwave_end = [&](unsigned int w) { return (unsigned int)(((unsigned long long)per_src * (w + 1)) / kBcastWaves); };
+  unsigned int dwave = 0;
+  uint32_t sz_next = (mode == 1) ? sizes_of(0) : 0u;
   for (unsigned int f = 0; f < nitems; ++f) {
+    if (collective && per_src && f == per_src) trace_mark(a.c, 3);   // first received field decoded
     if (mode == 2 && f % per_src == 0) {   // first item of the next source: its CTA of the same index must be done
-      const int src = (r + (int)(f / per_src)) % n;
-      if (src != r && !cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, 1u << src, 0xA0)) return;
+      const int src = (r + 1 + (int)(f / per_src)) % n;
+      if (!cta_wait_sources(sync, a.c, a.c.arena[r], 0, r, 1u << src, 0xA0)) return;
       sz_next = sizes_of(f);               // (re)read now that the source's bytes are visible
     }
+    if (mode == 3) {                        // first item of the next wave of the root's CTA of the same index
+      bool waited = false;
+      while (dwave < kBcastWaves && (dwave ? dwave_end(dwave - 1) : 0u) <= f) {
+        if (dwave_end(dwave) > (dwave ? dwave_end(dwave - 1) : 0u)) {
+          if (!cta_wait_sources(sync, a.c, a.c.arena[r], (int)dwave, r, 1u << a.root, 0xA0)) return;
+          waited = true;
+        }
+        ++dwave;
+      }
+      if (waited) sz_next = sizes_of(f);
+    }
     const uint32_t sz = sz_next;
-    sz_next = (mode == 2 && (f + 1) % per_src == 0) ? 0u : sizes_of(f + 1);
+    // no prefetch across a source or wave boundary: those bytes may not have arrived yet
+    const bool boundary = (mode == 2 && (f + 1) % per_src == 0) ||
+                          (mode == 3 && dwave < kBcastWaves && (dwave ? dwave_end(dwave - 1) : 0u) <= f + 1);
+    sz_next = boundary ? 0u : sizes_of(f + 1);
     if (!valid(f)) continue;
     uint32_t off = __reduce_add_sync(0xffffffffu, sz);
     if (off > (uint32_t)(kClusterSize * kTileCap)) {   // damaged size words: stay inside the slot and flag it
       off = 0;
       if (threadIdx.x == 0 && a.c.status) atomicOr(a.c.status + CCB_STATUS_FLAGS, CCB_ST_TIMEOUT);
     }
-    const int q = mode == 2 ? (r + (int)(f / per_src)) % n : a.root;
+    const int q = mode == 2 ? (r + 1 + (int)(f / per_src)) % n : a.root;
     float* out = a.f[lr].out + (mode == 2 ? (size_t)q * a.nx * a.ny * a.nz : 0);
     unpack_tile(reinterpret_cast<const unsigned char*>(group_of(f)) + kGroupHeader + off, reinterpret_cast<int*>(vals2[0]), a,
                 out, tile_coord(a, (cl + (f % per_src) * ncl) * kClusterSize + k));
   }
+  if (collective) trace_mark(a.c, 4);
   if (mode == 3) end_handshake(sync, a.c, r);
 }
 
@@ -683,6 +767,16 @@ extern "C" int ccb_sz_collective(ccb_comm* c, const float* const* send, float* c
   a.root = root < 0 ? 0 : root;
   a.rank0 = ccb_comm_rank(c);
   a.nlocal = nlocal;
+  {  // progress steps of a broadcast: every step costs the root a system fence
+    static int waves = 0;
+    if (!waves) {
+      const char* e = getenv("CCB_SZ_BCAST_WAVES");
+      waves = e ? atoi(e) : 2;
+      if (waves < 1) waves = 1;
+      if (waves > (int)kMaxBcastWaves) waves = (int)kMaxBcastWaves;
+    }
+    a.bcast_waves = (unsigned int)waves;
+  }
   if (d_used) cudaMemsetAsync(d_used, 0, sizeof(unsigned long long) * nlocal, stream);
   return sz_launch(a, nlocal, device_sms(), true, stream);
 }
