@@ -37,7 +37,8 @@ def parse():
     ap.add_argument("--bytes", type=int, default=256 << 20, help="message bytes per rank")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "f16"])
     ap.add_argument("--codec", default="int8", choices=["int8", "fp8", "none", "int8_g256"])
-    ap.add_argument("--algo", default="twoshot", choices=["auto", "twoshot", "oneshot", "ring", "tree", "nvls"])
+    ap.add_argument("--algo", default="tune", choices=["tune", "auto", "twoshot", "oneshot", "ring", "tree", "nvls"],
+                    help="tune: time two-shot and ring on this message before the warm-up and keep the faster")
     ap.add_argument("--error-feedback", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -83,6 +84,10 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    requested = args.algo
+    if args.algo == "tune":
+        args.algo = comm.tune_all_reduce(x, y, codec=args.codec, algos=("twoshot", "ring")) if world > 1 else "twoshot"
 
     def step():
         comm.all_reduce(x, y, codec=args.codec, algo=args.algo, error_feedback=ef)
@@ -200,6 +205,7 @@ def main():
             "config": {"model": "gradient-like buffer: Laplace(0,1e-3) + 0.1% x100 outliers",
                        "global_batch": args.bytes * world, "seq_len": count,
                        "message_bytes_per_rank": args.bytes, "codec": args.codec, "algo": args.algo,
+                       "algo_selection": "measured before warm-up: two-shot vs ring" if requested == "tune" else "fixed",
                        "error_feedback": bool(args.error_feedback),
                        "parallelism": f"dp{world}", "l2": "inputs (256 MiB) larger than L2, no flush needed",
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},

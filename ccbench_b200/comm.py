@@ -163,9 +163,48 @@ class Communicator:
         ep, et = self._ptrs(error_feedback, "error_feedback")
         if et is not None and any(e.dtype != torch.float32 or e.numel() != st[0].numel() for e in et):
             raise ValueError("error_feedback must be float32 with send's element count")
+        if algo == "auto":   # a measured choice for this shape, when tune_all_reduce() made one
+            algo = getattr(self, "_tuned", {}).get((st[0].numel(), st[0].dtype, codec), "auto")
         _check(lib().ccb_all_reduce(self._h, sp, rp, st[0].numel(), self._dtype(st), _code(op, K.OPS),
                                     _code(codec, K.CODECS), _code(algo, K.ALGOS), ep, self._stream()))
         return recv
+
+    def tune_all_reduce(self, send: Tensors, recv: Tensors, *, codec="int8", algos=("twoshot", "ring", "oneshot"),
+                        iters: int = 3) -> str:
+        """Times each algorithm on these very buffers (CUDA events, maximum over the ranks
+        of an initialised torch.distributed group), remembers the fastest for this
+        (element count, dtype, codec) and returns its name; all_reduce(algo="auto") then
+        uses it. Every rank must call it with the same arguments. Candidates that do not
+        fit the arena (one-shot on large messages) are skipped."""
+        import torch.distributed as dist
+
+        _, st = self._ptrs(send, "send")
+        dist_up = dist.is_available() and dist.is_initialized() and self.nlocal == 1 and self.nranks > 1
+        best, best_t = "auto", float("inf")
+        for algo in algos:
+            wire = wire_bytes(codec, st[0].dtype, st[0].numel())
+            if algo == "oneshot" and wire * self.nranks > self.arena_bytes // 2 - (1 << 20):
+                continue
+            for _ in range(2):
+                self.all_reduce(send, recv, codec=codec, algo=algo)
+            if dist_up:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(iters):
+                self.all_reduce(send, recv, codec=codec, algo=algo)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=st[0].device)
+            if dist_up:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            if t.item() < best_t:
+                best, best_t = algo, t.item()
+        if not hasattr(self, "_tuned"):
+            self._tuned = {}
+        self._tuned[(st[0].numel(), st[0].dtype, codec)] = best
+        return best
 
     def reduce_scatter(self, send: Tensors, recv: Tensors, *, op="sum", codec="int8",
                        error_feedback: Optional[Tensors] = None):
