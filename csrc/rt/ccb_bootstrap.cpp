@@ -2,6 +2,8 @@
 
 #include <errno.h>
 #include <poll.h>
+#include <sys/mman.h>
+#include <stdio.h>
 #include <string.h>
 #include <sys/socket.h>
 #include <sys/un.h>
@@ -232,3 +234,44 @@ bool Bootstrap::barrier(int seq) {
 }
 
 }  // namespace ccb
+
+// Test hook (host only, no CUDA call): one rendezvous as the communicator set-up does
+// it. Every rank all-gathers its rank number together with a descriptor of an anonymous file that
+// holds one byte (its rank), reads the byte through each received descriptor, then
+// passes the barrier unless `skip_barrier` is set (a rank that leaves between the two
+// steps). Returns 0 and the sum of the bytes read, or 1 with the reason in `err`
+// when a step ran out of `timeout_ms`: how a rank that never joins, or that dies
+// half-way, shows up on the others, on the host, before any kernel is launched.
+extern "C" int ccb_test_bootstrap_exchange(int rank, int nranks, const char* tag, int timeout_ms, int skip_barrier,
+                                           int* sum_out, char* err, int err_len) {
+  auto fail = [&](const std::string& why) {
+    if (err && err_len > 0) snprintf(err, (size_t)err_len, "%s", why.c_str());
+    return 1;
+  };
+  ccb::Bootstrap b(rank, nranks, tag ? tag : "test", timeout_ms);
+  if (!b.ok()) return fail("listen: " + b.error());
+  const int mfd = memfd_create("ccb_test", MFD_CLOEXEC);
+  if (mfd < 0) return fail("memfd_create");
+  const unsigned char mine = (unsigned char)rank;
+  if (write(mfd, &mine, 1) != 1) return fail("write");
+  std::vector<ccb::BootMsg> all;
+  const int32_t me = rank;
+  const bool ok = b.all_gather(1, 0, &me, sizeof(me), mfd, &all);
+  close(mfd);
+  if (!ok) return fail("all_gather: " + b.error());
+  int sum = rank;
+  for (int r = 0; r < nranks; ++r) {
+    if (r == rank) continue;
+    const ccb::BootMsg& m = all[(size_t)r];
+    int32_t who = -1;
+    if (m.payload.size() == sizeof(who)) memcpy(&who, m.payload.data(), sizeof(who));
+    unsigned char byte = 0xff;
+    if (who != r || m.fd < 0 || pread(m.fd, &byte, 1, 0) != 1 || byte != (unsigned char)r) return fail("bad message from a peer");
+    close(m.fd);
+    sum += byte;
+  }
+  if (sum_out) *sum_out = sum;
+  if (skip_barrier) return 0;
+  if (!b.barrier(1)) return fail("barrier: " + b.error());
+  return 0;
+}
