@@ -124,6 +124,7 @@ def main(argv=None):
 
                 fl = flush if size < args.flush_below else None
                 t = timed(fn, args.iters, args.warmup, world, dev, fl) - timed(fn_copy, args.iters, args.warmup, world, dev, fl)
+                fn()  # leave the collective's result in y for the error column
             else:
                 codec, algo = parts[0], parts[1] if len(parts) > 1 else "auto"
                 comm.set_waves(int(parts[2]) if len(parts) > 2 else 0)

@@ -89,9 +89,9 @@ __global__ void __launch_bounds__(kThreads, 2) nvls_allreduce_kernel(const __gri
       }
     }
   }
-  __threadfence_system();
+  // the barrier orders every thread's stores before thread 0's single fence
   __syncthreads();
-  if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 0, r, b), c.epoch);
+  if (threadIdx.x == 0) signal_peers(c, ((1u << n) - 1u) & ~(1u << r), 0, r, b);
   if (!cta_wait_sources(sync, c, my, 0, r, 0xffu, 0x80)) return;
 
   // 2. own shard: reduce in the switch, broadcast through the switch
@@ -108,9 +108,8 @@ __global__ void __launch_bounds__(kThreads, 2) nvls_allreduce_kernel(const __gri
       }
     }
   }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < n && threadIdx.x != r) signal_flag(flag_ptr(c.arena[threadIdx.x], 1, r, b), c.epoch);
+  if (threadIdx.x == 0) signal_peers(c, ((1u << n) - 1u) & ~(1u << r), 1, r, b);
   if (!cta_wait_sources(sync, c, my, 1, r, 0xffu, 0x90)) return;
 
   // 3. copy out of the own arena
