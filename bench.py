@@ -67,6 +67,9 @@ def main():
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local_rank)
+    # host buffers and copy threads next to this GPU's PCIe root (matters for the end-to-end number)
+    from ccbench_b200.utils.numa import bind_to_gpu_node
+    numa = bind_to_gpu_node(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
@@ -211,7 +214,7 @@ def main():
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},
             "algbw": algbw, "ref_definition_bw": 2 * algbw, "compression_ratio": wire_ratio(args.codec, dtype),
             "rel_l2_error": rel_l2, "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "e2e": e2e, "gpu_launches": launches,
+            "e2e": e2e, "gpu_launches": launches, "host_numa_binding": numa,
         }
         print(json.dumps(line), flush=True)
     comm.close()
