@@ -1,0 +1,28 @@
+"""Small host utilities: NUMA binding, clock sampler parsing."""
+import os
+
+from ccbench_b200.utils import numa
+from ccbench_b200.utils.clocks import ClockSampler
+
+
+def test_cpulist_parsing():
+    assert numa._parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert numa._parse_cpulist("") == set()
+
+
+def test_binding_without_a_gpu_changes_nothing():
+    before = os.sched_getaffinity(0)
+    assert numa.bind_to_gpu_node(0)["node"] == -1
+    assert os.sched_getaffinity(0) == before
+
+
+def test_clock_summary_reads_nvidia_smi_rows(tmp_path):
+    s = ClockSampler([0, 1], 100)
+    f = tmp_path / "clocks.csv"
+    f.write_text("0, 1965, 1965, 412.3, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n"
+                 "1, 1950, 1965, 640.0, 0x0000000000000000, Not Active, Not Active, Not Active, Not Active\n"
+                 "0, 1935, 1965, 800.1, 0x0000000000000004, Not Active, Not Active, Not Active, Active\n")
+    s.file = open(f, "r+")
+    out = s.summary()
+    assert out["sm_mhz"] == 1950 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"] and out["samples"] == 3
+    assert s.gpu_index == "0,1"
