@@ -32,12 +32,43 @@ def gpu_numa_node(device_index: int) -> int:
         return -1
 
 
+def topo_cpu_affinity(device_index: int, topo_text: str | None = None) -> set[int]:
+    """CPU affinity of a GPU as `nvidia-smi topo -m` reports it (read-only query): the
+    fallback for hosts (containers) whose sysfs does not tell the NUMA node."""
+    import re
+    import shutil
+    import subprocess
+
+    if topo_text is None:
+        exe = shutil.which("nvidia-smi")
+        if not exe:
+            return set()
+        try:
+            topo_text = subprocess.run([exe, "topo", "-m"], capture_output=True, text=True, timeout=20).stdout
+        except Exception:
+            return set()
+    topo_text = re.sub(r"\x1b\[[0-9;]*m", "", topo_text)
+    for line in topo_text.splitlines():
+        cells = line.split()
+        if cells and cells[0] == f"GPU{device_index}":
+            for c in cells[1:]:
+                if re.fullmatch(r"\d+(-\d+)?(,\d+(-\d+)?)*", c) and ("-" in c or "," in c):
+                    return _parse_cpulist(c)
+    return set()
+
+
 def bind_to_gpu_node(device_index: int) -> dict:
-    """Returns what was done: {"node": n, "cpus": count} or {"node": -1}."""
+    """Returns what was done: {"node": n, "cpus": count}, {"node": -1, "cpus": count,
+    "source": "nvidia-smi topo"} when only the topology table knew, or {"node": -1}."""
     try:
         node = gpu_numa_node(device_index)
         if node < 0:
-            return {"node": -1}
+            cpus = topo_cpu_affinity(device_index)
+            allowed = os.sched_getaffinity(0) & cpus
+            if not allowed or allowed == os.sched_getaffinity(0):
+                return {"node": -1}
+            os.sched_setaffinity(0, allowed)
+            return {"node": -1, "cpus": len(allowed), "source": "nvidia-smi topo"}
         with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
             cpus = _parse_cpulist(f.read())
         allowed = os.sched_getaffinity(0) & cpus

@@ -48,12 +48,16 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
 
   // ---- send: block (r -> p). Dispatch gathers rows through perm; combine sends the
   // ---- contiguous block of rows that came from origin p (transposed counts).
-  size_t send_row_off = 0;  // dispatch: offset into perm of the rows for destination p
-  for (int p = 0; p < n; ++p) {
+  // Destinations are visited starting with the next rank, (r + 1) % n, ..., r: at any moment
+  // every rank stores to a different peer, so no inbound link takes all the traffic.
+  for (int jd = 1; jd <= n; ++jd) {
+    const int p = (r + jd) % n;
     const size_t rows = a.combine ? a.cnt[p][r] : a.cnt[r][p];
-    size_t base_row = 0;
-    if (a.combine)
-      for (int s = 0; s < p; ++s) base_row += a.cnt[s][r];
+    size_t base_row = 0, send_row_off = 0;  // combine: first row of origin p; dispatch: offset into perm
+    for (int s = 0; s < p; ++s) {
+      base_row += a.cnt[s][r];
+      send_row_off += a.cnt[r][s];
+    }
     char* slot = c.arena[p] + area + (size_t)r * a.slot_bytes;
     const size_t units = rows * upr;
     for (size_t t = b; t * kWarps < units; t += G) {
@@ -67,7 +71,6 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
       C::encode(v, pk);
       C::store(slot, pad, j * H + col, pk);
     }
-    if (!a.combine) send_row_off += rows;
   }
   __syncthreads();
   // the combine's receiver gathers rows written by any CTA, its own rank's included,
@@ -76,9 +79,13 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
 
   if (!a.combine) {
     // ---- dispatch receive: rows of source q land at recv row (sum_{s<q} cnt[s][r]) + j
-    if (!cta_wait_sources(sync, c, my, 0, r, 0xffu, 0xB0)) return;
-    size_t row0 = 0;
-    for (int q = 0; q < n; ++q) {
+    // own rows first (nothing to wait for), then each source as its flag arrives, in the
+    // order in which the sources reach this rank
+    for (int jq = 0; jq < n; ++jq) {
+      const int q = (r - jq + n) % n;
+      if (q != r && !cta_wait_sources(sync, c, my, 0, r, 1u << q, 0xB0)) return;
+      size_t row0 = 0;
+      for (int s = 0; s < q; ++s) row0 += a.cnt[s][r];
       const size_t units = a.cnt[q][r] * upr;
       const char* slot = my + area + (size_t)q * a.slot_bytes;
       for (size_t t = b; t * kWarps < units; t += G) {
@@ -91,7 +98,6 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
         C::decode(pk, d);
         store16<T>(dst + (row0 + j) * H, col, H, d);
       }
-      row0 += a.cnt[q][r];
     }
     return;
   }

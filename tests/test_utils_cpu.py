@@ -10,6 +10,15 @@ def test_cpulist_parsing():
     assert numa._parse_cpulist("") == set()
 
 
+def test_topology_table_fallback():
+    topo = ("\tGPU0\tGPU1\tNIC0\tCPU Affinity\tNUMA Affinity\tGPU NUMA ID\n"
+            "GPU0\t X \tNV18\tSYS\t0-55,112-167\t0\t\tN/A\n"
+            "GPU1\tNV18\t X \tSYS\t56-111,168-223\t1\t\tN/A\n")
+    assert numa.topo_cpu_affinity(0, topo) == set(range(0, 56)) | set(range(112, 168))
+    assert 56 in numa.topo_cpu_affinity(1, topo) and 0 not in numa.topo_cpu_affinity(1, topo)
+    assert numa.topo_cpu_affinity(5, topo) == set()
+
+
 def test_binding_without_a_gpu_changes_nothing():
     before = os.sched_getaffinity(0)
     assert numa.bind_to_gpu_node(0)["node"] == -1
