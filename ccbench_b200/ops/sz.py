@@ -69,6 +69,70 @@ def _collective(comm, send, recv, eb, root, used):
     return recv
 
 
+# -------------------------------------------------------------- container --
+# A compressed buffer in device memory is a row of fixed-capacity group slots
+# ([8 x u32 tile sizes][tiles back to back], GROUP_STRIDE bytes each), mostly empty. For
+# storage or for transports that want one contiguous message it is packed into a
+# self-describing container:
+#   [u32 magic 'CCSZ'][u32 version = 2][u32 nx][u32 ny][u32 nz][f32 eb][f32 step][u32 ngroups]
+#   [u64 payload bytes][u32 used bytes of each group (header included)] [the used bytes of every group]
+MAGIC, VERSION = 0x5A534343, 2
+GROUP_STRIDE, GROUP_HEADER, HEADER_BYTES = 66112, 32, 40
+
+
+def to_container(buf: torch.Tensor, shape, eb: float) -> torch.Tensor:
+    """Packs the group slots of `buf` (as returned by compress) into one contiguous uint8
+    tensor on the same device. Plain tensor operations, no extra kernel."""
+    nz, ny, nx = shape
+    ngroups = buf.numel() // GROUP_STRIDE
+    slots = buf.view(ngroups, GROUP_STRIDE)
+    sizes = slots[:, :GROUP_HEADER].contiguous().view(torch.int32).to(torch.int64).sum(dim=1) + GROUP_HEADER
+    keep = torch.arange(GROUP_STRIDE, device=buf.device).unsqueeze(0) < sizes.unsqueeze(1)
+    payload = slots[keep]
+    step = torch.tensor(2.0 * eb, dtype=torch.float32) * (1 - 2.0 ** -10)
+    head = torch.zeros(HEADER_BYTES, dtype=torch.uint8)
+    head[0:20].view(torch.int32).copy_(torch.tensor([MAGIC, VERSION, nx, ny, nz], dtype=torch.int32))
+    head[20:28].view(torch.float32).copy_(torch.tensor([eb, step.item()], dtype=torch.float32))
+    head[28:32].view(torch.int32).copy_(torch.tensor([ngroups], dtype=torch.int32))
+    head[32:40].view(torch.int64).copy_(torch.tensor([payload.numel()], dtype=torch.int64))
+    return torch.cat([head.to(buf.device), sizes.to(torch.int32).view(torch.uint8), payload])
+
+
+def from_container(blob: torch.Tensor):
+    """Inverse of to_container: returns (buffer of group slots, shape, eb)."""
+    head = blob[:HEADER_BYTES].cpu()
+    magic, version, nx, ny, nz = head[0:20].view(torch.int32).tolist()
+    if magic != MAGIC or version != VERSION:
+        raise ValueError(f"not a ccb-sz v{VERSION} container (magic {magic:#x}, version {version})")
+    eb = head[20:24].view(torch.float32).item()
+    ngroups = head[28:32].view(torch.int32).item()
+    nbytes = head[32:40].view(torch.int64).item()
+    if ngroups * GROUP_STRIDE != capacity((nz, ny, nx)):
+        raise ValueError("container header does not match its dimensions")
+    sizes = blob[HEADER_BYTES:HEADER_BYTES + 4 * ngroups].contiguous().view(torch.int32).to(torch.int64)
+    payload = blob[HEADER_BYTES + 4 * ngroups:]
+    if payload.numel() != nbytes or int(sizes.sum().item()) != nbytes or int(sizes.max().item()) > GROUP_STRIDE:
+        raise ValueError("container payload is damaged")
+    buf = torch.zeros(ngroups, GROUP_STRIDE, dtype=torch.uint8, device=blob.device)
+    keep = torch.arange(GROUP_STRIDE, device=blob.device).unsqueeze(0) < sizes.unsqueeze(1)
+    buf[keep] = payload
+    return buf.view(-1), (nz, ny, nx), eb
+
+
+def save(path, field: torch.Tensor, eb: float) -> int:
+    """Compresses `field` and writes the container to `path`; returns the file size."""
+    buf, _ = compress(field, eb)
+    blob = to_container(buf, field.shape, eb).cpu().numpy()
+    blob.tofile(path)
+    return int(blob.size)
+
+
+def load(path, device="cuda") -> torch.Tensor:
+    blob = torch.from_numpy(np.fromfile(path, dtype=np.uint8)).to(device)
+    buf, shape, eb = from_container(blob)
+    return decompress(buf, shape, eb)
+
+
 # ------------------------------------------------------------------ oracle --
 def restate(field: np.ndarray, eb: float):
     """NumPy restatement: returns (reconstruction fp32, packed bytes per the format)."""

@@ -82,3 +82,26 @@ def test_fused_all_gather_and_broadcast(n):
             assert np.array_equal(out[r].cpu().numpy(), want[n - 1])
     finally:
         comm.close()
+
+
+def test_container_roundtrip_and_file(tmp_path):
+    from ccbench_b200.models.workloads import smooth_field
+
+    f = smooth_field(72, seed=5, device="cuda")[:, :60, :68].contiguous()   # ragged tiles on two axes
+    eb = 1e-3 * (f.max() - f.min()).item()
+    buf, used = sz.compress(f, eb)
+    blob = sz.to_container(buf, f.shape, eb)
+    assert blob.numel() < f.numel() * 4 / 3
+    ngroups = buf.numel() // sz.GROUP_STRIDE
+    assert blob.numel() == sz.HEADER_BYTES + 4 * ngroups + int(used.item()) + ngroups * sz.GROUP_HEADER
+    back, shape, eb2 = sz.from_container(blob)
+    assert tuple(shape) == tuple(f.shape) and eb2 == float(torch.tensor(eb, dtype=torch.float32))
+    want = sz.decompress(buf, f.shape, eb)
+    assert torch.equal(sz.decompress(back, shape, eb2), want)
+    n = sz.save(tmp_path / "field.ccsz", f, eb)
+    assert n == blob.numel()
+    assert torch.equal(sz.load(tmp_path / "field.ccsz"), want)
+    bad = blob.clone()
+    bad[0] ^= 0xFF
+    with pytest.raises(ValueError):
+        sz.from_container(bad)
