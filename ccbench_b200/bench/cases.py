@@ -7,6 +7,8 @@ process. `python -m ccbench_b200.bench.cases --case NAME [--launches 3]`.
   sz_compress            error-bounded codec, 384^3 fp32 field (226 MB)
   sz_decompress
   moe_dispatch_fp8       4096 tokens x 4096 hidden bf16, 4 ranks on this GPU
+  allreduce_ring_int8_8ranks   ring kernel, eight ranks on this GPU, 16 Mi bf16 each
+  allgather_fp8_8ranks   exchange kernel, eight ranks on this GPU, 4 Mi bf16 each
 """
 from __future__ import annotations
 
@@ -41,6 +43,20 @@ def main(argv=None):
         ys = [torch.empty_like(x) for x in xs]
         for _ in range(a.launches):
             comm.all_reduce(xs, ys, codec="int8", algo="twoshot")
+    elif a.case == "allreduce_ring_int8_8ranks":
+        n = 8
+        comm = Communicator.local(n, arena_bytes=96 << 20)
+        xs = [gradient_like(16 << 20, torch.bfloat16, seed=r, device=dev) for r in range(n)]
+        ys = [torch.empty_like(x) for x in xs]
+        for _ in range(a.launches):
+            comm.all_reduce(xs, ys, codec="int8", algo="ring")
+    elif a.case == "allgather_fp8_8ranks":
+        n = 8
+        comm = Communicator.local(n, arena_bytes=96 << 20)
+        xs = [normal(4 << 20, torch.bfloat16, seed=r, device=dev) for r in range(n)]
+        ys = [torch.empty(n * (4 << 20), dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        for _ in range(a.launches):
+            comm.all_gather(xs, ys, codec="fp8")
     elif a.case in ("sz_compress", "sz_decompress"):
         f = smooth_field(384, device=dev)
         eb = 1e-4 * (f.max() - f.min()).item()
