@@ -28,3 +28,12 @@ def build(verbose: bool = False) -> None:
                 root / "csrc/wrappers/perf_helper_nccl.c", root / "csrc/core/perf.c"]
     if all(p.exists() for p in perf_src):
         nb.cc(libs / "libperfnccl.so", perf_src, shared=True, libs=["-ldl", "-lpthread"], verbose=verbose, compiler="cc")
+    # example compression wrapper with its own kernels (4-bit / 8-bit groups, SDP4Bit chunk layout)
+    sdp = root / "userconfig/wrapper_code_examples/compression/sdp4bit/sdp4bit.cu"
+    out = libs / "libsdp4bit.so"
+    if sdp.exists() and nb._newer(out, [sdp]):
+        import shutil
+
+        nvcc = shutil.which("nvcc") or str(nb.CUDA / "bin" / "nvcc")
+        nb._run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-shared", "-Xcompiler", "-fPIC",
+                 *(f"-I{i}" for i in nb.INC), sdp, "-o", out], verbose)
