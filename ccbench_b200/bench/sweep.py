@@ -56,6 +56,29 @@ def timed(fn, iters, warmup, world, dev, flush=None):
     return t.item() * 1e3  # us
 
 
+def done_keys(csv_path: str, nranks: int, dtype: str) -> set:
+    """(msg_size, algo, codec) of the rows a result CSV already holds for this job shape:
+    what --resume skips, so that an interrupted sweep continues where it stopped."""
+    keys = set()
+    if not csv_path or not os.path.exists(csv_path):
+        return keys
+    with open(csv_path) as f:
+        for line in f:
+            p = line.strip().split(",")
+            if len(p) >= 6 and p[0].isdigit() and p[1] == str(nranks) and p[2] == dtype:
+                keys.add((int(p[0]), p[3], p[4]))
+    return keys
+
+
+def variant_key(var: str):
+    """(algo column, codec column) of a --variants entry, as the rows print them."""
+    parts = var.split(":")
+    if parts[0] == "nccl":
+        return "nccl", "none"
+    algo = parts[1] if len(parts) > 1 else "auto"
+    return algo + "".join(":" + q for q in parts[2:]), parts[0]
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     # the long names are the ones to use under torch.distributed.run, whose own parser
@@ -72,6 +95,7 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--arena-mb", type=int, default=2048)
     ap.add_argument("--csv", default="")
+    ap.add_argument("--resume", action="store_true", help="skip the (size, algorithm, codec) rows already in --csv")
     ap.add_argument("--flush-below", type=int, default=64 << 20,
                     help="messages smaller than this are timed per call with an L2 flush in between")
     args = ap.parse_args(argv)
@@ -97,6 +121,7 @@ def main(argv=None):
             s *= args.factor
     flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)  # 640 MB > L2
     rows = []
+    done = done_keys(args.csv, world, args.dtype) if args.resume else set()
     header = "msg_size,nranks,dtype,algo,codec,time_us,algbw,busbw,ref_bw,ratio,rel_l2"
     if rank == 0:
         print(header, flush=True)
@@ -109,6 +134,8 @@ def main(argv=None):
         if world > 1:
             dist.all_reduce(exact)
         for var in args.variants.split(","):
+            if (count * es, *variant_key(var)) in done:   # every rank reads the same file: same decision everywhere
+                continue
             parts = var.split(":")
             if parts[0] == "nccl":
                 if world == 1:
