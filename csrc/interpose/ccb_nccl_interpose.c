@@ -19,6 +19,11 @@
  *   CCB_MOVE_CODEC=...           codec of AllGather/Broadcast/AlltoAll (default = CCB_CODEC)
  *   CCB_ALGO=auto|twoshot|oneshot|ring|tree|nvls
  *   CCB_ERROR_FEEDBACK=1         keep a residual per (communicator, buffer, count)
+ *   CCB_P2P_CODEC=int8|fp8|int4  also compress ncclSend / ncclRecv (default: off, plain NCCL).
+ *                                The bytes still travel by NCCL point-to-point (pipeline
+ *                                traffic stays there); one encode kernel before the send and
+ *                                one decode kernel after the receive, stream-ordered, no host
+ *                                synchronisation, also inside ncclGroupStart/End.
  *   CCB_MIN_BYTES=N              smaller messages go to NCCL (default 0)
  *   CCB_VERBOSE=1                log decisions to stderr                         */
 #define _GNU_SOURCE
@@ -59,7 +64,7 @@ static pthread_mutex_t g_lock = PTHREAD_MUTEX_INITIALIZER;
 static __thread int g_group_depth;
 
 static struct {
-    int inited, disabled, codec, move_codec, algo, ef, verbose;
+    int inited, disabled, codec, move_codec, algo, ef, verbose, p2p_codec;
     size_t min_bytes;
 } cfg;
 
@@ -100,6 +105,7 @@ static void load_cfg(void) {
     }
     cfg.ef = (e = getenv("CCB_ERROR_FEEDBACK")) && *e == '1';
     cfg.min_bytes = (e = getenv("CCB_MIN_BYTES")) ? (size_t)strtoull(e, NULL, 10) : 0;
+    cfg.p2p_codec = codec_by_name(getenv("CCB_P2P_CODEC"), CCB_CODEC_NONE);
     cfg.inited = 1;
     LOGV("config: disabled=%d codec=%d move_codec=%d algo=%d error_feedback=%d min_bytes=%zu", cfg.disabled, cfg.codec,
          cfg.move_codec, cfg.algo, cfg.ef, cfg.min_bytes);
@@ -120,6 +126,8 @@ typedef ncclResult_t (*fn_bcast)(void *, size_t, ncclDataType_t, int, ncclComm_t
 typedef ncclResult_t (*fn_reduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, int, ncclComm_t, cudaStream_t);
 typedef ncclResult_t (*fn_commdestroy)(ncclComm_t);
 typedef ncclResult_t (*fn_group)(void);
+typedef ncclResult_t (*fn_send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+typedef ncclResult_t (*fn_recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
 typedef ncclResult_t (*fn_commint)(const ncclComm_t, int *);
 typedef int (*fn_ext_a2a)(const void *, size_t, ncclDataType_t, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
 typedef int (*fn_ext_rooted)(const void *, size_t, ncclDataType_t, void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
@@ -131,6 +139,8 @@ REAL(ncclBcast, fn_bcast)
 REAL(ncclReduce, fn_reduce)
 REAL(ncclCommDestroy, fn_commdestroy)
 REAL(ncclCommAbort, fn_commdestroy)
+REAL(ncclSend, fn_send)
+REAL(ncclRecv, fn_recv)
 REAL(ncclGroupStart, fn_group)
 REAL(ncclGroupEnd, fn_group)
 REAL(ncclCommUserRank, fn_commint)
@@ -394,6 +404,73 @@ int ncclGather(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, v
     return f ? f(sendbuf, sendcount, sendtype, recvbuf, recvcount, recvtype, root, comm, stream) : 1;
 }
 
+/* ------------------------------------------------------- point-to-point --
+ * Compressed ncclSend / ncclRecv (CCB_P2P_CODEC): encode into a stream-ordered temporary,
+ * move the wire bytes with the real NCCL call, decode after the receive. Inside a group NCCL
+ * only records the call and runs it at the outermost ncclGroupEnd, so the decode and the
+ * release of the temporaries are deferred to that point as well. Both ends must run with the
+ * same setting; the wire size is a function of (codec, dtype, count) only. */
+#define MAX_PENDING 256
+typedef struct {
+    void *wire, *user; /* user != NULL: a receive to decode into user */
+    size_t count;
+    int dtype;
+    cudaStream_t stream;
+} p2p_pending;
+static __thread p2p_pending g_pending[MAX_PENDING];
+static __thread int g_npending;
+
+static ncclResult_t p2p_finish(const p2p_pending *p) {
+    ncclResult_t rc = ncclSuccess;
+    if (p->user && ccb_decode(cfg.p2p_codec, p->dtype, p->wire, p->count, p->user, p->stream) != CCB_OK) rc = ncclInternalError;
+    cudaFreeAsync(p->wire, p->stream);
+    return rc;
+}
+static int p2p_wanted(size_t count, ncclDataType_t dt, cudaStream_t stream) {
+    load_cfg();
+    if (cfg.disabled || cfg.p2p_codec == CCB_CODEC_NONE || dtype_of(dt) < 0 || count == 0) return 0;
+    if (count * (dtype_of(dt) == CCB_F32 ? 4 : 2) < cfg.min_bytes || stream_is_capturing(stream)) return 0;
+    return g_group_depth == 0 || g_npending < MAX_PENDING;
+}
+
+ncclResult_t ncclSend(const void *sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {
+    fn_send f = get_ncclSend();
+    if (!f) return ncclInternalError;
+    if (!p2p_wanted(count, datatype, stream)) return f(sendbuff, count, datatype, peer, comm, stream);
+    const int dt = dtype_of(datatype);
+    const size_t wb = (size_t)ccb_wire_bytes(cfg.p2p_codec, dt, count);
+    p2p_pending p = {NULL, NULL, count, dt, stream};
+    if (cudaMallocAsync(&p.wire, wb, stream) != cudaSuccess) return ncclUnhandledCudaError;
+    if (ccb_encode(cfg.p2p_codec, dt, sendbuff, count, p.wire, stream) != CCB_OK) {
+        cudaFreeAsync(p.wire, stream);
+        return ncclInternalError;
+    }
+    ncclResult_t rc = f(p.wire, wb, ncclUint8, peer, comm, stream);
+    if (g_group_depth > 0 && rc == ncclSuccess) g_pending[g_npending++] = p;
+    else p2p_finish(&p);
+    return rc;
+}
+
+ncclResult_t ncclRecv(void *recvbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {
+    fn_recv f = get_ncclRecv();
+    if (!f) return ncclInternalError;
+    if (!p2p_wanted(count, datatype, stream)) return f(recvbuff, count, datatype, peer, comm, stream);
+    const int dt = dtype_of(datatype);
+    const size_t wb = (size_t)ccb_wire_bytes(cfg.p2p_codec, dt, count);
+    p2p_pending p = {NULL, recvbuff, count, dt, stream};
+    if (cudaMallocAsync(&p.wire, wb, stream) != cudaSuccess) return ncclUnhandledCudaError;
+    ncclResult_t rc = f(p.wire, wb, ncclUint8, peer, comm, stream);
+    if (rc != ncclSuccess) {
+        cudaFreeAsync(p.wire, stream);
+        return rc;
+    }
+    if (g_group_depth > 0) {
+        g_pending[g_npending++] = p;
+        return ncclSuccess;
+    }
+    return p2p_finish(&p);
+}
+
 ncclResult_t ncclGroupStart(void) {
     ++g_group_depth;
     fn_group f = get_ncclGroupStart();
@@ -402,7 +479,15 @@ ncclResult_t ncclGroupStart(void) {
 ncclResult_t ncclGroupEnd(void) {
     if (g_group_depth > 0) --g_group_depth;
     fn_group f = get_ncclGroupEnd();
-    return f ? f() : ncclInternalError;
+    ncclResult_t rc = f ? f() : ncclInternalError;
+    if (g_group_depth == 0 && g_npending > 0) { /* the grouped transfers are enqueued now */
+        for (int i = 0; i < g_npending; ++i) {
+            const ncclResult_t r2 = (rc == ncclSuccess) ? p2p_finish(&g_pending[i]) : (cudaFreeAsync(g_pending[i].wire, g_pending[i].stream), ncclSuccess);
+            if (rc == ncclSuccess) rc = r2;
+        }
+        g_npending = 0;
+    }
+    return rc;
 }
 
 static void drop_comm(ncclComm_t comm) {

@@ -4,7 +4,8 @@
  * 28-250); here every collective is ONE ncclGroupStart/End, so NCCL schedules all
  * peers at once over NVSwitch. Symbols are resolved through the dynamic linker at
  * call time, so a preloaded interposer that wraps ncclSend/ncclRecv/ncclCommUserRank
- * is honoured. */
+ * is honoured; the calls carry the caller's element type and count (not bytes), so that
+ * such an interposer can tell floating-point payloads from the rest. */
 #include <stdint.h>
 #include <string.h>
 
@@ -47,11 +48,11 @@ int ncclScatter(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, 
                     return 1;
                 }
             } else {
-                TRY(ncclSend(src, sb, ncclUint8, p, comm, stream));
+                TRY(ncclSend(src, sendcount, sendtype, p, comm, stream));
             }
         }
     } else {
-        TRY(ncclRecv(recvbuf, rb, ncclUint8, root, comm, stream));
+        TRY(ncclRecv(recvbuf, recvcount, recvtype, root, comm, stream));
     }
     return ncclGroupEnd() != ncclSuccess;
 }
@@ -71,11 +72,11 @@ int ncclGather(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, v
                     return 1;
                 }
             } else {
-                TRY(ncclRecv(dst, rb, ncclUint8, p, comm, stream));
+                TRY(ncclRecv(dst, recvcount, recvtype, p, comm, stream));
             }
         }
     } else {
-        TRY(ncclSend(sendbuf, sb, ncclUint8, root, comm, stream));
+        TRY(ncclSend(sendbuf, sendcount, sendtype, root, comm, stream));
     }
     return ncclGroupEnd() != ncclSuccess;
 }
@@ -98,8 +99,8 @@ int ncclAllGatherv(const void *sendbuf, int sendcount, ncclDataType_t sendtype, 
             }
             continue;
         }
-        TRY(ncclSend(sendbuf, (size_t)sendcount * se, ncclUint8, p, comm, stream));
-        TRY(ncclRecv(dst, (size_t)recvcounts[p] * re, ncclUint8, p, comm, stream));
+        TRY(ncclSend(sendbuf, (size_t)sendcount, sendtype, p, comm, stream));
+        TRY(ncclRecv(dst, (size_t)recvcounts[p], recvtype, p, comm, stream));
     }
     return ncclGroupEnd() != ncclSuccess;
 }
@@ -111,7 +112,7 @@ int ncclScatterv(const void *sendbuf, const int sendcounts[], const int displs[]
     (void)d_displs;
     int rank, n;
     if (rank_size(comm, &rank, &n)) return 1;
-    const size_t se = esize(sendtype), re = esize(recvtype);
+    const size_t se = esize(sendtype);
     if (ncclGroupStart() != ncclSuccess) return 1;
     if (rank == root) {
         for (int p = 0; p < n; ++p) {
@@ -123,11 +124,11 @@ int ncclScatterv(const void *sendbuf, const int sendcounts[], const int displs[]
                     return 1;
                 }
             } else if (bytes) {
-                TRY(ncclSend(src, bytes, ncclUint8, p, comm, stream));
+                TRY(ncclSend(src, (size_t)sendcounts[p], sendtype, p, comm, stream));
             }
         }
     } else if (recvcount > 0) {
-        TRY(ncclRecv(recvbuf, (size_t)recvcount * re, ncclUint8, root, comm, stream));
+        TRY(ncclRecv(recvbuf, (size_t)recvcount, recvtype, root, comm, stream));
     }
     return ncclGroupEnd() != ncclSuccess;
 }
@@ -149,8 +150,8 @@ int ncclAllToAll(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype,
             }
             continue;
         }
-        TRY(ncclSend(src, sb, ncclUint8, p, comm, stream));
-        TRY(ncclRecv(dst, rb, ncclUint8, p, comm, stream));
+        TRY(ncclSend(src, sendcount, sendtype, p, comm, stream));
+        TRY(ncclRecv(dst, recvcount, recvtype, p, comm, stream));
     }
     return ncclGroupEnd() != ncclSuccess;
 }

@@ -75,3 +75,19 @@ def test_result_csv_has_the_reference_columns(tmp_path):
     _run(tmp_path, "allreduce", ["-L", "65536,1048576", "-i", "2", "-w", "1", "-d", "float", "-c", "-o", str(out_csv)])
     rows = list(csv.reader(open(out_csv)))
     assert len(rows) >= 3 and "msg_size" in ",".join(rows[0]).lower().replace(" ", "_")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="point-to-point needs two GPUs")
+@pytest.mark.parametrize("test", ["allgatherv", "scatterv"])
+def test_compressed_point_to_point_under_the_interposer(tmp_path, test):
+    """ncclSend / ncclRecv compressed by the interposer inside ncclGroupStart/End, bytes moved
+    by NCCL. The report is rank 0's: in scatterv that is the root, whose own share is a plain
+    copy, so only allgatherv must show a quantisation error there."""
+    args = ["-L", "1048576", "-i", "2", "-w", "1", "-d", "float", "-v", "-t", "1e30", "-e", "rel_l2"]
+    plain = _run(tmp_path, test, args, preload=["libccb_nccl.so"], env={"CCB_VERBOSE": "1"})
+    packed = _run(tmp_path, test, args, preload=["libccb_nccl.so"], env={"CCB_P2P_CODEC": "int8", "CCB_VERBOSE": "1"})
+    assert max(_metric(plain, "rel_l2")) < 1e-6
+    rel = _metric(packed, "rel_l2")
+    assert max(rel) < 0.02, rel
+    if test == "allgatherv":
+        assert max(rel) > 0, "the receive path was not compressed"
