@@ -168,3 +168,32 @@ int nvmlDeviceGetPowerUsage(dev_t d,unsigned*p){*p=700000;return 0;}
     assert rows[0] == "timestamp_sec,gpu_util,mem_util,mem_used,temperature,pcie_gen,pcie_width,sm_clock,power"
     v = rows[1].split(",")
     assert v[1:] == ["42.000000", "7.000000", "3.000000", "55.000000", "5.000000", "16.000000", "1965.000000", "700.000000"]
+
+
+def test_run_script_order_of_operations(tmp_path):
+    """What the run script must do, in the order that matters: clean stale state, export the
+    user's environment before LD_PRELOAD, preload compression : communication : extensions,
+    phase 1, clean the rendezvous files, phase 2 with the perf wrapper FIRST, exit with the
+    larger of the two return codes."""
+    cfg = load_config(CFG)
+    cfg.job_choice = "local"
+    text = runscript.generate(cfg, ROOT)
+    pos = lambda needle, start=0: text.index(needle, start)  # noqa: E731
+    clean = pos('rm -f "$BENCH_DIR/nccl_id_file/"*')
+    user_env = pos("export CCB_CODEC=")
+    preload = pos('LD_PRELOAD="${LD_PRELOAD:-}"')
+    comm_lib, ext_lib = pos("libccb_nccl.so"), pos("libnccl_extensions.so")
+    phase1 = pos("PHASE1_PRELOAD=")
+    between = pos('rm -f "$BENCH_DIR/nccl_id_file/"*', phase1)
+    phase2 = pos("Phase 2")
+    perf = pos("libperfnccl.so", phase2)
+    rejoin = pos("$PHASE1_PRELOAD", perf)
+    gendata = pos("export PERF_GENDATA_TARGETS=", phase2)
+    final = pos("if [ $BENCH_RC1 -ge $BENCH_RC2 ]; then exit $BENCH_RC1; else exit $BENCH_RC2; fi")
+    assert clean < user_env < preload < comm_lib < ext_lib < phase1 < between < phase2 < perf < rejoin < gendata < final
+    assert "perf_files" in text[:clean + 400] and 'rm -rf "$PERF_OUTPUT_DIR"' in text
+    assert "daemon_signals" in text and ".signal" in text
+    # the benchmark binary's arguments follow the reference's argv
+    for phase in (1, 2):
+        joined = f" {runscript.bench_args(cfg, phase)} "
+        assert (" -m " in joined or " -L " in joined) and " -i " in joined and " -w " in joined and " -d " in joined
