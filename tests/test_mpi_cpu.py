@@ -63,6 +63,31 @@ def test_error_bounded_cpu_codec_and_perf_rows(tmp_path):
     assert all(float(r.split(",")[1]) >= 0 for r in rows[1:])
 
 
+@pytest.mark.parametrize("rate,limit", [(16, 2e-4), (8, 5e-2)])
+def test_fixed_rate_cpu_codec(tmp_path, rate, limit):
+    pre = f"{LIBS / 'libperfmpi.so'}:{LIBS / 'libmpi_zfp.so'}:{LIBS / 'libplain_mpi_compress.so'}"
+    out = _run(2, "allreduce", pre, ["-L", "262144", "-i", "2", "-w", "1", "-d", "float", "-v", "-t", "1e30", "-e", "rel_l2"],
+               env={"MPI_ZFP_RATE": str(rate), "PERF_OUTPUT_DIR": str(tmp_path / "pf")}, cwd=tmp_path, tag=f"zf{rate}")
+    rel = float(out.split("rel_l2:")[1].split()[0])
+    assert 0 < rel < limit, out
+    rows = (tmp_path / "pf" / "perf_function_0.csv").read_text().splitlines()
+    cols = rows[0].split(",")
+    ratio = [float(r.split(",")[cols.index("compression_ratio")]) for r in rows[1:] if r.startswith("mpi_compress")]
+    # fixed rate: 32 bits in, `rate` bits (+ 16 per 64 values) out, whatever the data
+    assert all(abs(x - 32.0 / (rate + 0.25)) < 0.05 * 32.0 / rate for x in ratio), ratio
+
+
+def test_collectives_and_codec_in_one_library(tmp_path):
+    pre = str(LIBS / "libmpi_zccl_wrapper.so")
+    for test in ("allreduce", "bcast", "allgather", "scatter"):
+        out = _run(3, test, pre, ["-L", "200000", "-i", "1", "-w", "1", "-d", "float", "-v", "-t", "1e30", "-e", "max_abs_err"],
+                   env={"ZCCL_TOL": "1e-3"}, cwd=tmp_path, tag=f"zc{test[:3]}")
+        err = float(out.split("max_abs_err:")[1].split()[0])
+        assert err <= 3 * 1e-3 * 3 + 1e-3, (test, out)
+        if test in ("allreduce", "allgather"):   # the report is rank 0's; a root keeps its own exact copy
+            assert err > 0, (test, out)
+
+
 def test_pingpong_csv_layout(tmp_path):
     _run(2, "pingpong", args=["-L", "1024,65536", "-i", "3", "-w", "1", "-c", "-o", str(tmp_path / "pp.csv")], cwd=tmp_path, tag="pp")
     rows = (tmp_path / "pp.csv").read_text().splitlines()
