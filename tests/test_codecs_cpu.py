@@ -49,3 +49,35 @@ def test_reference_wire_layout():
     assert inv.numel() == 3 and q.numel() == 600
     d = q[:256].float() / inv[0]
     assert (d - x[:256]).abs().max() <= x[:256].abs().max() / 254 * 1.001
+
+
+def test_wire_bytes_of_every_codec():
+    """Slot size = payload of the padded element count + its scales, rounded to 256 bytes."""
+    import torch
+
+    from ccbench_b200.comm import wire_bytes
+
+    def want(codec, es, count):
+        pad = -(-count // 512) * 512
+        b = {"none": pad * es, "int8": pad + pad // 128 * 4, "int8_g256": pad + pad // 256 * 4, "fp8": pad + pad // 32,
+             "int4": pad // 2 + pad // 128 * 4}[codec]
+        return -(-b // 256) * 256
+
+    for codec in ("none", "int8", "int8_g256", "fp8", "int4"):
+        for dt, es in ((torch.float32, 4), (torch.bfloat16, 2)):
+            for count in (1, 512, 513, 100000, (1 << 20) + 7):
+                assert wire_bytes(codec, dt, count) == want(codec, es, count), (codec, dt, count)
+
+
+def test_int4_restatement_properties():
+    import torch
+
+    from ccbench_b200.ops import codecs as C
+
+    x = torch.randn(1000, generator=torch.Generator().manual_seed(0))
+    y = C.roundtrip(x, "int4")
+    grp = torch.cat([x, torch.zeros(24)]).view(-1, 128).abs().amax(dim=1)
+    step = (grp / 7).repeat_interleave(128)[:1000]
+    assert ((x - y).abs() <= 0.5 * step + 1e-7).all()
+    assert torch.equal(C.roundtrip(y, "int4"), y)          # idempotent: codes survive a second trip
+    assert abs(C.wire_ratio("int4", torch.bfloat16) - 2 / (0.5 + 4 / 128)) < 1e-9
