@@ -139,7 +139,10 @@ def main(args) -> int:
             t_us = float(m.group(3))
             algbw = args.bytes / (t_us * 1e-6) / 1e9
             line = {
-                "metric": "compressed_allreduce_busbw", "value": algbw * 2 * (world - 1) / world, "unit": "GB/s",
+                "metric": "compressed_allreduce_busbw", "value": algbw * 2 * (world - 1) / world * world, "unit": "GB/s",
+                "value_definition": "whole-job aggregate: per-GPU bus bandwidth (bytes/t * 2(n-1)/n) summed over the n GPUs; "
+                                    "busbw_per_gpu holds the per-GPU figure",
+                "busbw_per_gpu": algbw * 2 * (world - 1) / world,
                 "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t_us / 1e3,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
                 "impl": "reference",
@@ -164,7 +167,8 @@ def main(args) -> int:
         line["mse"] = float(mm.group(1)) if mm else None
         per_iter = max(wall2 - wall1, 0.0) / extra
         if per_iter > 0:
-            line["e2e"] = {"value": args.bytes / per_iter / 1e9 * 2 * (world - 1) / world, "unit": "GB/s",
+            line["e2e"] = {"value": args.bytes / per_iter / 1e9 * 2 * (world - 1) / world * world, "unit": "GB/s",
+                           "busbw_per_gpu": args.bytes / per_iter / 1e9 * 2 * (world - 1) / world,
                            "ms_per_step": per_iter * 1e3, "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": 0,
                            "note": "wall-clock slope between runs of K and K+40 iterations of the reference loop"}
     if rank == 0:

