@@ -46,14 +46,7 @@ def collect(perf_dir, metric, device_class=None, t_min=None, t_max=None):
     return series
 
 
-def plot(series, metric, path, bins=200):
-    try:
-        import matplotlib
-    except ImportError:
-        print("matplotlib is not installed: no PNG written")
-        return None
-    matplotlib.use("Agg")
-    import matplotlib.pyplot as plt
+def _grid(series, bins):
     import numpy as np
 
     names = sorted(series)
@@ -64,6 +57,21 @@ def plot(series, metric, path, bins=200):
         for t, v in series[n]:
             j = min(bins - 1, int((t - t0) / max(t1 - t0, 1e-9) * bins))
             grid[i, j] = v
+    return names, t0, t1, grid
+
+
+def plot(series, metric, path, bins=200):
+    names, t0, t1, grid = _grid(series, bins)
+    try:
+        import matplotlib
+    except ImportError:   # headless host without matplotlib: plain PNG + legend file
+        from ._png import heatmap
+
+        heatmap(path, grid, names, f"time, {t0:.3f} s .. {t1:.3f} s in {bins} bins", metric, cell=(4, 18))
+        return path
+    matplotlib.use("Agg")
+    import matplotlib.pyplot as plt
+
     fig, ax = plt.subplots(figsize=(10, max(2, 0.3 * len(names) + 1)))
     im = ax.imshow(grid, aspect="auto", extent=[t0, t1, len(names), 0], cmap="viridis")
     ax.set_yticks([i + 0.5 for i in range(len(names))])
@@ -72,6 +80,7 @@ def plot(series, metric, path, bins=200):
     fig.colorbar(im, ax=ax, label=metric)
     fig.tight_layout()
     fig.savefig(path, dpi=120)
+    return path
 
 
 def main(argv=None):

@@ -35,27 +35,31 @@ def main(argv=None):
     if not table:
         print("no perf CSVs under", a.perf_dir)
         return 1
-    try:
-        import matplotlib
-    except ImportError:
-        print("matplotlib is not installed: no PNG written")
-        return None
-    matplotlib.use("Agg")
-    import matplotlib.pyplot as plt
     import numpy as np
 
     ranks = sorted(table, key=lambda r: int(r) if r.isdigit() else 0)
     grid = np.array([[table[r].get(f, [0.0, 0])[0] * 1e3 for f in funcs] for r in ranks])
-    fig, ax = plt.subplots(figsize=(max(4, len(funcs)), max(3, 0.4 * len(ranks) + 2)))
-    im = ax.imshow(grid, aspect="auto", cmap="magma")
-    ax.set_xticks(range(len(funcs)))
-    ax.set_xticklabels(funcs, rotation=45, ha="right", fontsize=7)
-    ax.set_yticks(range(len(ranks)))
-    ax.set_yticklabels(ranks)
-    ax.set_ylabel("rank")
-    fig.colorbar(im, ax=ax, label="total time (ms)")
-    fig.tight_layout()
-    fig.savefig(a.save, dpi=120)
+    try:
+        import matplotlib
+    except ImportError:   # headless host without matplotlib: plain PNG + legend file
+        from ._png import heatmap
+
+        heatmap(a.save, grid, [f"rank {r}" for r in ranks], "functions, left to right: " + ", ".join(funcs), "total time (ms)",
+                cell=(48, 24))
+    else:
+        matplotlib.use("Agg")
+        import matplotlib.pyplot as plt
+
+        fig, ax = plt.subplots(figsize=(max(4, len(funcs)), max(3, 0.4 * len(ranks) + 2)))
+        im = ax.imshow(grid, aspect="auto", cmap="magma")
+        ax.set_xticks(range(len(funcs)))
+        ax.set_xticklabels(funcs, rotation=45, ha="right", fontsize=7)
+        ax.set_yticks(range(len(ranks)))
+        ax.set_yticklabels(ranks)
+        ax.set_ylabel("rank")
+        fig.colorbar(im, ax=ax, label="total time (ms)")
+        fig.tight_layout()
+        fig.savefig(a.save, dpi=120)
     for r in ranks:
         print(r, {f: (round(v[0] * 1e3, 3), v[1]) for f, v in table[r].items()})
     return 0
