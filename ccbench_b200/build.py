@@ -11,3 +11,7 @@ def build_all(verbose: bool = False) -> None:
     except ImportError:
         return
     build_c_targets(verbose=verbose)
+    # what the reference's compile_all.sh also leaves behind: the metric override library
+    from .wrapper_build import register_metrics
+
+    register_metrics(verbose=verbose)
