@@ -27,6 +27,10 @@ def launch_command(cfg: BenchConfig, check: bool = True) -> str:
     n = cfg.nprocs
     fwd = "".join(f" -x {k}" for k in cfg.env) if cfg.env else ""
     if cfg.arch == "mpi":
+        if cfg.job_choice == "local" and not shutil.which("mpirun"):
+            # no MPI on this host: the binaries are linked against the bundled single-host MPI
+            # subset, which takes its ranks from the local launcher's environment
+            return f"python3 -m ccbench_b200.launch -n {n} --"
         if check and not shutil.which("mpirun"):
             raise RuntimeError("communication_arch=mpi requires mpirun")
         if cfg.job_choice == "srun":
@@ -235,9 +239,12 @@ def generate(cfg: BenchConfig, bench_dir: str | os.PathLike, check_launcher: boo
         _preload_block(L, "perf", cfg.perf)
         L('LD_PRELOAD="${LD_PRELOAD:+$LD_PRELOAD${PHASE1_PRELOAD:+:}}$PHASE1_PRELOAD"')
         L("export LD_PRELOAD")
-        if cfg.benchmark_type == "app_gendata" or cfg.gendata_targets:
+        if cfg.benchmark_type == "app_gendata" and cfg.gendata_targets:
+            # capture runs only: the perf wrapper dumps the named calls' buffers and ends the run
             L(f"export PERF_GENDATA_TARGETS={shlex.quote(cfg.gendata_targets)}")
-            L('export PERF_GENDATA_OUTPUT_DIR="${PERF_GENDATA_OUTPUT_DIR:-$BENCH_DIR/gendata}"')
+            where = cfg.output_bin_path or "gendata"
+            where = where if os.path.isabs(where) else "$BENCH_DIR/" + where
+            L(f'export PERF_GENDATA_OUTPUT_DIR="${{PERF_GENDATA_OUTPUT_DIR:-{where}}}"')
             L('export PERF_GENDATA_DONE_DIR="$BENCH_DIR/daemon_signals"')
             L('mkdir -p "$PERF_GENDATA_OUTPUT_DIR"')
         L("PHASE2_DAEMON_PIDS=()")

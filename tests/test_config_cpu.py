@@ -188,7 +188,12 @@ def test_run_script_order_of_operations(tmp_path):
     phase2 = pos("Phase 2")
     perf = pos("libperfnccl.so", phase2)
     rejoin = pos("$PHASE1_PRELOAD", perf)
-    gendata = pos("export PERF_GENDATA_TARGETS=", phase2)
+    assert "PERF_GENDATA_TARGETS=" not in text.replace("PERF_GENDATA_TARGETS PERF", "")   # capture runs only
+    cfg2 = load_config(CFG)
+    cfg2.job_choice, cfg2.benchmark_type = "local", "app_gendata"
+    text2 = runscript.generate(cfg2, ROOT)
+    assert text2.index("export PERF_GENDATA_TARGETS=") > text2.index("Phase 2")
+    gendata = rejoin + 1
     final = pos("if [ $BENCH_RC1 -ge $BENCH_RC2 ]; then exit $BENCH_RC1; else exit $BENCH_RC2; fi")
     assert clean < user_env < preload < comm_lib < ext_lib < phase1 < between < phase2 < perf < rejoin < gendata < final
     assert "perf_files" in text[:clean + 400] and 'rm -rf "$PERF_OUTPUT_DIR"' in text
