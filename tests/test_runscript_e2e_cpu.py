@@ -24,7 +24,8 @@ def test_generated_script_runs_both_phases(tmp_path):
     cfg.phase1_measure = cfg.phase2_measure = 2
     cfg.validation_enabled, cfg.validation_metrics = True, "rel_l2,max_abs_err"
     cfg.output_csv, cfg.output_csv_path = True, str(tmp_path / "results" / "allreduce.csv")
-    cfg.daemons_enabled = False
+    cfg.daemons_enabled, cfg.selected_daemons, cfg.poll_interval = True, ["cpu"], 0.2
+    cfg.phase1_daemons, cfg.phase2_daemons = ["cpu"], ["cpu"]
     cfg.comp = dataclasses.replace(cfg.comp, mode=1, library_paths=["bin/libs/libmpi_int8.so"])
     cfg.comm = dataclasses.replace(cfg.comm, mode=1, library_paths=["bin/libs/libplain_mpi_compress.so"])
     cfg.perf = dataclasses.replace(cfg.perf, mode=1, library_paths=["bin/libs/libperfmpi.so"])
@@ -43,3 +44,7 @@ def test_generated_script_runs_both_phases(tmp_path):
     assert len(perf) == 2
     names = {line.split(",")[0] for line in perf[0].read_text().splitlines()[1:]}
     assert {"MPI_Allreduce", "mpi_compress"} <= names
+    # the monitoring daemon was started and stopped around the phases and left its samples
+    cpu = sorted((tmp_path / "perf_files").glob("perf_cpu*.csv"))
+    assert cpu and cpu[0].read_text().startswith("timestamp_sec,")
+    assert subprocess.run(["pgrep", "-x", "daemon_cpu"], capture_output=True).returncode != 0, "daemon left running"
