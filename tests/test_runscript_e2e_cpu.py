@@ -48,3 +48,38 @@ def test_generated_script_runs_both_phases(tmp_path):
     cpu = sorted((tmp_path / "perf_files").glob("perf_cpu*.csv"))
     assert cpu and cpu[0].read_text().startswith("timestamp_sec,")
     assert subprocess.run(["pgrep", "-x", "daemon_cpu"], capture_output=True).returncode != 0, "daemon left running"
+
+
+def test_capture_run_dumps_buffers_that_feed_a_later_run(tmp_path):
+    """benchmark_type = app_gendata: the application (here the MPI all-reduce driver started by
+    the local launcher) runs under the perf wrapper, which dumps the buffers of the named call
+    and ends the run; the dump directory then serves as a folder data source."""
+    build_c_targets()
+    cfg = load_config(ROOT / "userconfig" / "config_in_jsonc")
+    exe = ROOT / "bin" / "mpi" / "allreduce" / "allreduce"
+    cfg.arch, cfg.benchmark_type, cfg.test_name = "mpi", "app_gendata", "allreduce"
+    cfg.job_choice, cfg.nodes, cfg.tasks_per_node = "local", 1, 2
+    cfg.app_command = f"python3 -m ccbench_b200.launch -n 2 -- {exe} -L 65536 -i 4 -w 1 -d float"
+    cfg.gendata_targets = "MPI_Allreduce:2"
+    cfg.output_bin_path = str(tmp_path / "captured")
+    cfg.daemons_enabled = False
+    cfg.comp = dataclasses.replace(cfg.comp, mode=0)
+    cfg.comm = dataclasses.replace(cfg.comm, mode=0)
+    cfg.perf = dataclasses.replace(cfg.perf, mode=1, library_paths=["bin/libs/libperfmpi.so"])
+    cfg.env = {"CCB_MINIMPI_JOB": f"cap{os.getpid()}"}
+    script = runscript.write(cfg, ROOT, out_dir=tmp_path)
+    env = dict(os.environ, PERF_OUTPUT_DIR=str(tmp_path / "perf_files"))
+    env.pop("LD_PRELOAD", None)
+    env.pop("PERF_GENDATA_OUTPUT_DIR", None)
+    r = subprocess.run(["bash", str(script)], capture_output=True, text=True, timeout=600, env=env)
+    dumps = sorted((tmp_path / "captured").rglob("rank_*.bin"))
+    assert dumps, r.stdout[-3000:] + r.stderr[-2000:]
+    assert {p.name for p in dumps} == {"rank_0.bin", "rank_1.bin"} and dumps[0].parent.name == "MPI_Allreduce_000002"
+    assert dumps[0].stat().st_size == 65536
+    # the dump directory as the data source of a plain run
+    from ccbench_b200 import launch
+
+    rcs, outs = launch.launch(2, [str(exe), "-L", "65536", "-i", "1", "-w", "0", "-d", "float", "-v", "-f", str(dumps[0].parent)], "",
+                              {"CCB_MINIMPI_JOB": f"use{os.getpid()}", "DS_TYPE": "folder", "DS_SUFFIX": ".bin", "DS_FORMAT": "binary"},
+                              cwd=str(tmp_path), timeout=120, capture=True)
+    assert rcs == [0, 0] and "Correct: YES" in outs[0], outs[0][-1500:]
