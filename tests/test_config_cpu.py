@@ -202,3 +202,19 @@ def test_run_script_order_of_operations(tmp_path):
     for phase in (1, 2):
         joined = f" {runscript.bench_args(cfg, phase)} "
         assert (" -m " in joined or " -L " in joined) and " -i " in joined and " -w " in joined and " -d " in joined
+
+
+@pytest.mark.parametrize("script,produces", [
+    ("register_metrics.sh", "bin/libs/validation.so"),
+    ("register_job_device_mapper.sh", "bin/libs/libjob_device_mapper.so"),
+    ("register_daemons.sh", "bin/daemons/daemon_cpu"),
+    ("compile_all.sh", "bin/libs/libnccl_extensions.so"),
+])
+def test_script_entry_points(script, produces):
+    """The shell entry points keep the reference's names and leave its build outputs behind."""
+    from pathlib import Path
+
+    root = Path(ROOT)
+    r = subprocess.run(["bash", str(root / "scripts" / script)], capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert (root / produces).exists()
