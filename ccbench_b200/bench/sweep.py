@@ -14,7 +14,6 @@ from __future__ import annotations
 
 import argparse
 import os
-import sys
 
 import torch
 import torch.distributed as dist

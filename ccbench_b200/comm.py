@@ -13,7 +13,6 @@ entry points that this class wraps.
 from __future__ import annotations
 
 import ctypes
-import os
 import uuid
 from typing import Optional, Sequence, Union
 

@@ -6,7 +6,6 @@ run_codes/benchmark-core/src/utils.c:162-223); with no datasets available the
 shapes and distributions are generated here instead."""
 from __future__ import annotations
 
-import math
 
 import torch
 
