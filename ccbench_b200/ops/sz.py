@@ -133,6 +133,129 @@ def load(path, device="cuda") -> torch.Tensor:
     return decompress(buf, shape, eb)
 
 
+# ------------------------------------------------------------ CPU codec --
+# The same format in NumPy, for hosts without a GPU (reading a stored field, checking a
+# transfer) and as a second statement of the layout. Slow (seconds for 128^3): not a
+# benchmark path.
+_QMAX = float(1 << 22)
+
+
+def _step(eb: float):
+    two_eb = np.float32(2.0) * np.float32(eb) * (np.float32(1.0) - np.float32(2.0 ** -10))
+    return two_eb, np.float32(1.0) / two_eb
+
+
+def _tiles_of(a: np.ndarray):
+    """[nz, ny, nx] -> [tiles, 8, 8, 32], zero-padded, tiles ordered x fastest."""
+    nz, ny, nx = a.shape
+    a = np.pad(a, ((0, (-nz) % TZ), (0, (-ny) % TY), (0, (-nx) % TX)))
+    Z, Y, X = a.shape
+    return a.reshape(Z // TZ, TZ, Y // TY, TY, X // TX, TX).transpose(0, 2, 4, 1, 3, 5).reshape(-1, TZ, TY, TX)
+
+
+def _pack_tile_cpu(vals: np.ndarray, two_eb, inv, eb32) -> bytes:
+    s = vals * inv
+    bad = ~np.isfinite(vals).all() or not (np.abs(s) < _QMAX).all()
+    if not bad:
+        q = np.rint(s).astype(np.int64)
+        r = q.astype(np.float32) * two_eb
+        half = np.float32(0.5) * two_eb
+        q = q + ((vals - r) > half) - ((r - vals) > half)
+        bad = bool((np.abs(vals - q.astype(np.float32) * two_eb) > eb32).any())
+    if bad:
+        return bytes([255] + [0] * 63) + vals.astype("<f4").tobytes()
+    d = q.copy()
+    d[1:] -= q[:-1]
+    d2 = d.copy()
+    d2[:, 1:] -= d[:, :-1]
+    d3 = d2.copy()
+    d3[:, :, 1:] -= d2[:, :, :-1]
+    u = ((d3 << 1) ^ (d3 >> 63)) & 0xFFFFFFFF
+    rows = u.reshape(TZ, TY, TX // 8, 8).transpose(0, 3, 1, 2).reshape(TZ * 8, 32)   # row 8z+e, thread 4y+xq
+    mx = rows.max(axis=1)
+    widths = np.array([int(m).bit_length() for m in mx], dtype=np.uint8)
+    out = bytearray(widths.tobytes())
+    weights = (np.uint64(1) << np.arange(32, dtype=np.uint64))
+    for row, w in zip(rows.astype(np.uint64), widths):
+        for j in range(int(w)):
+            out += int((((row >> np.uint64(j)) & np.uint64(1)) * weights).sum()).to_bytes(4, "little")
+    out += bytes((-len(out)) % 16)
+    return bytes(out)
+
+
+def encode_cpu(field: np.ndarray, eb: float) -> np.ndarray:
+    """Compresses a [nz, ny, nx] fp32 array into the container format (uint8 array)."""
+    x = np.ascontiguousarray(field, dtype=np.float32)
+    nz, ny, nx = x.shape
+    two_eb, inv = _step(eb)
+    eb32 = np.float32(eb)
+    tiles = _tiles_of(x)
+    packed = [_pack_tile_cpu(t, two_eb, inv, eb32) for t in tiles]
+    ngroups = (len(packed) + 7) // 8
+    groups, used = [], []
+    for g in range(ngroups):
+        mine = packed[8 * g:8 * g + 8]
+        sizes = np.zeros(8, dtype="<u4")
+        sizes[:len(mine)] = [len(p) for p in mine]
+        groups.append(sizes.tobytes() + b"".join(mine))
+        used.append(len(groups[-1]))
+    payload = b"".join(groups)
+    head = np.zeros(HEADER_BYTES, dtype=np.uint8)
+    head[0:20].view("<i4")[:] = [MAGIC, VERSION, nx, ny, nz]
+    head[20:28].view("<f4")[:] = [eb32, two_eb]
+    head[28:32].view("<i4")[:] = [ngroups]
+    head[32:40].view("<i8")[:] = [len(payload)]
+    return np.concatenate([head, np.array(used, dtype="<u4").view(np.uint8), np.frombuffer(payload, dtype=np.uint8)])
+
+
+def decode_cpu(blob: np.ndarray) -> np.ndarray:
+    """Inverse of encode_cpu (and of to_container on a GPU-compressed buffer)."""
+    blob = np.asarray(blob, dtype=np.uint8)
+    magic, version, nx, ny, nz = blob[0:20].view("<i4").tolist()
+    if magic != MAGIC or version != VERSION:
+        raise ValueError("not a ccb-sz v2 container")
+    two_eb = blob[24:28].view("<f4")[0]
+    ngroups = int(blob[28:32].view("<i4")[0])
+    used = blob[HEADER_BYTES:HEADER_BYTES + 4 * ngroups].view("<u4").astype(np.int64)
+    body = blob[HEADER_BYTES + 4 * ngroups:]
+    if int(used.sum()) != body.size:
+        raise ValueError("container payload is damaged")
+    tx, ty, tz = -(-nx // TX), -(-ny // TY), -(-nz // TZ)
+    ntiles = tx * ty * tz
+    out = np.zeros((tz * TZ, ty * TY, tx * TX), dtype=np.float32)
+    shifts = np.arange(32, dtype=np.uint64)
+    pos = 0
+    for g in range(ngroups):
+        grp = body[pos:pos + int(used[g])]
+        pos += int(used[g])
+        sizes = grp[:GROUP_HEADER].view("<u4")
+        off = GROUP_HEADER
+        for k in range(8):
+            tile = 8 * g + k
+            if tile >= ntiles or sizes[k] == 0:
+                continue
+            t = grp[off:off + int(sizes[k])]
+            off += int(sizes[k])
+            if t[0] == 255:
+                vals = t[64:64 + 4 * TZ * TY * TX].view("<f4").reshape(TZ, TY, TX)
+            else:
+                widths = t[:64]
+                words = t[64:].view("<u4").astype(np.uint64)
+                rows = np.zeros((TZ * 8, 32), dtype=np.uint64)
+                w0 = 0
+                for r, w in enumerate(widths):
+                    for j in range(int(w)):
+                        rows[r] |= ((words[w0 + j] >> shifts) & np.uint64(1)) << np.uint64(j)
+                    w0 += int(w)
+                u = rows.reshape(TZ, 8, TY, TX // 8).transpose(0, 2, 3, 1).reshape(TZ, TY, TX).astype(np.int64)
+                d = (u >> 1) ^ -(u & 1)
+                q = d.cumsum(axis=2).cumsum(axis=1).cumsum(axis=0)
+                vals = q.astype(np.float32) * two_eb
+            z0, y0, x0 = tile // (tx * ty) * TZ, tile // tx % ty * TY, tile % tx * TX
+            out[z0:z0 + TZ, y0:y0 + TY, x0:x0 + TX] = vals
+    return out[:nz, :ny, :nx].copy()
+
+
 # ------------------------------------------------------------------ oracle --
 def restate(field: np.ndarray, eb: float):
     """NumPy restatement: returns (reconstruction fp32, packed bytes per the format)."""

@@ -41,3 +41,36 @@ def test_damaged_containers_are_refused():
     wrong[4] = 9   # version
     with pytest.raises(ValueError):
         sz.from_container(wrong)
+
+
+def test_cpu_codec_round_trip_matches_the_restatement():
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    zz, yy, xx = np.meshgrid(np.arange(20), np.arange(13), np.arange(70), indexing="ij")
+    field = (np.sin(zz / 5.0) * np.cos(yy / 3.0) + 0.01 * xx + 1e-3 * rng.standard_normal(zz.shape)).astype(np.float32)
+    eb = 1e-3
+    blob = sz.encode_cpu(field, eb)
+    recon, nbytes = sz.restate(field, eb)
+    back = sz.decode_cpu(blob)
+    assert back.shape == field.shape and np.array_equal(back, recon)
+    assert float(np.abs(back - field).max()) <= np.float32(eb)
+    ngroups = sz.capacity(field.shape) // sz.GROUP_STRIDE
+    assert blob.size == sz.HEADER_BYTES + 4 * ngroups + nbytes + ngroups * sz.GROUP_HEADER
+    # the tensor-side container reader accepts what the CPU encoder wrote
+    buf, shape, eb2 = sz.from_container(torch.from_numpy(blob))
+    assert tuple(shape) == field.shape and abs(eb2 - eb) < 1e-9
+    assert np.array_equal(sz.decode_cpu(sz.to_container(buf, shape, eb2).numpy()), recon)
+
+
+def test_cpu_codec_stores_unquantisable_tiles_raw():
+    import numpy as np
+
+    field = np.zeros((8, 8, 64), dtype=np.float32)
+    field[:, :, :32] = np.linspace(-1, 1, 8 * 8 * 32, dtype=np.float32).reshape(8, 8, 32)
+    field[3, 4, 40] = np.nan
+    field[1, 1, 50] = 3e30
+    blob = sz.encode_cpu(field, 1e-3)
+    back = sz.decode_cpu(blob)
+    assert np.array_equal(back[:, :, 32:], field[:, :, 32:], equal_nan=True)     # raw tile: bit exact
+    assert float(np.abs(back[:, :, :32] - field[:, :, :32]).max()) <= np.float32(1e-3)
