@@ -218,3 +218,16 @@ def test_script_entry_points(script, produces):
     r = subprocess.run(["bash", str(root / "scripts" / script)], capture_output=True, text=True, timeout=1200)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
     assert (root / produces).exists()
+
+
+def test_run_script_golden_file():
+    """The script for the shipped default configuration, local launcher, byte for byte. When a
+    change to the generator is intended, regenerate the golden file with the three lines
+    below and review its diff."""
+    from pathlib import Path
+
+    cfg = load_config(CFG)
+    cfg.job_choice = "local"
+    text = runscript.generate(cfg, Path("/opt/ccbench"))
+    golden = Path(ROOT) / "tests" / "golden" / "run_benchmark_local_default.sh"
+    assert text == golden.read_text(), "generated script differs from tests/golden/run_benchmark_local_default.sh"
