@@ -47,6 +47,12 @@ def main(argv=None) -> int:
         from . import runscript, wrapper_build
 
         cfg = load_config(a.config_dir)
+        wrong = cfg.problems(ROOT)
+        if wrong:
+            print("[build_script] the configuration cannot be used:", file=sys.stderr)
+            for w in wrong:
+                print("  - " + w, file=sys.stderr)
+            return 2
         if a.cmd == "build":
             if a.rebuild_bench:
                 from .native_build import build_c_targets

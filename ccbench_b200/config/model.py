@@ -105,6 +105,61 @@ class BenchConfig:
     def is_app(self) -> bool:
         return self.benchmark_type in ("app_trace", "app_gendata")
 
+    def problems(self, root: str | os.PathLike | None = None) -> list[str]:
+        """What is wrong with this configuration, in the user's words: one line per problem,
+        empty when it can be turned into a run script. `root` enables the checks that look
+        at the repository (benchmark binaries known, prebuilt libraries present)."""
+        out: list[str] = []
+        tests = ("allreduce", "allgather", "allgatherv", "alltoall", "bcast", "gather", "overlap", "pingpong", "reduce",
+                 "reducescatter", "scatter", "scatterv")
+        if self.arch not in ("mpi", "nccl"):
+            out.append(f"communication_arch {self.arch!r}: expected mpi or nccl (rccl has no benchmarks on this hardware)")
+        if not self.is_app and self.test_name not in tests:
+            out.append(f"benchmark_type {self.benchmark_type!r}: no benchmark named {self.test_name!r}; known: " + ", ".join(tests))
+        if self.is_app and not self.app_command.strip():
+            out.append(f"benchmark_type {self.benchmark_type} needs app_command")
+        if self.benchmark_type == "app_gendata" and not self.gendata_targets:
+            out.append("benchmark_type app_gendata needs gendata_capture.targets with at least one occurrence")
+        if self.job_choice not in ("slurm", "srun", "mpirun", "local"):
+            out.append(f"job_choice {self.job_choice!r}: expected slurm, srun, mpirun or local")
+        if self.nodes < 1 or self.tasks_per_node < 1:
+            out.append("slurm.resources.nodes and tasks_per_node must be at least 1")
+        for kind, sel in (("communication", self.comm), ("compression", self.comp), ("perf", self.perf)):
+            if sel.mode not in (0, 1, 2, 3):
+                out.append(f"{kind} selection: mode {sel.mode} is not one of 0 (off), 1 (prebuilt), 2 (build + link), 3 (build)")
+            elif sel.mode == 1 and not sel.library_paths:
+                out.append(f"{kind} selection: mode 1 needs library_paths")
+            elif sel.mode in (2, 3) and not (sel.source_files or sel.source_dirs):
+                out.append(f"{kind} selection: mode {sel.mode} needs source_files or source_dirs")
+            elif sel.mode in (2, 3) and not sel.output_name:
+                out.append(f"{kind} selection: mode {sel.mode} needs output_name")
+            if root is not None and sel.mode == 1:
+                for lib in sel.library_paths:
+                    p = Path(lib) if os.path.isabs(lib) else Path(root) / lib
+                    if not p.exists() and not str(lib).startswith("bin/libs/"):
+                        out.append(f"{kind} selection: library {lib} does not exist")
+        if self.msg_mode not in ("range", "list"):
+            out.append(f"message_sizes.mode {self.msg_mode!r}: expected range or list")
+        elif self.msg_mode == "list" and not self.msg_list:
+            out.append("message_sizes.mode list needs a non-empty list")
+        elif self.msg_mode == "range":
+            if self.msg_min < 1 or self.msg_max < self.msg_min:
+                out.append(f"message_sizes: min {self.msg_min} and max {self.msg_max} do not make a range")
+            if self.msg_incr_type not in ("multiply", "add"):
+                out.append(f"message_sizes.increment_type {self.msg_incr_type!r}: expected multiply or add")
+            elif self.msg_incr < (2 if self.msg_incr_type == "multiply" else 1):
+                out.append(f"message_sizes.increment {self.msg_incr} never reaches max")
+        if self.ds_type not in ("pattern", "file", "folder"):
+            out.append(f"data_source.type {self.ds_type!r}: expected pattern, file or folder")
+        elif self.ds_type in ("file", "folder") and not self.ds_file:
+            out.append(f"data_source.type {self.ds_type} needs file_path")
+        if min(self.phase1_measure, self.phase2_measure) < 1 or min(self.phase1_warmup, self.phase2_warmup) < 0:
+            out.append("iterations: measurement counts must be at least 1 and warm-up counts not negative")
+        for pct, name in ((self.stress_cpu_percent, "cpu_percent"), (self.stress_gpu_percent, "gpu_percent")):
+            if not 0 <= pct <= 100:
+                out.append(f"daemon stress.{name} {pct}: expected 0..100")
+        return out
+
 
 def load_config(config_dir: str | os.PathLike) -> BenchConfig:
     d = Path(config_dir)

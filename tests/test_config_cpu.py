@@ -231,3 +231,35 @@ def test_run_script_golden_file():
     text = runscript.generate(cfg, Path("/opt/ccbench"))
     golden = Path(ROOT) / "tests" / "golden" / "run_benchmark_local_default.sh"
     assert text == golden.read_text(), "generated script differs from tests/golden/run_benchmark_local_default.sh"
+
+
+def test_configuration_problems_are_named(tmp_path):
+    import dataclasses
+
+    cfg = load_config(CFG)
+    assert cfg.problems(ROOT) == []
+    cfg.arch, cfg.job_choice, cfg.msg_mode, cfg.msg_list = "rccl", "pbs", "list", []
+    cfg.comm = dataclasses.replace(cfg.comm, mode=7)
+    cfg.perf = dataclasses.replace(cfg.perf, mode=3, source_files=[], source_dirs=[])
+    cfg.ds_type, cfg.ds_file = "folder", ""
+    cfg.stress_gpu_percent = 250
+    text = "\\n".join(cfg.problems(ROOT))
+    for needle in ("communication_arch 'rccl'", "job_choice 'pbs'", "non-empty list", "mode 7", "needs source_files", "needs file_path", "250"):
+        assert needle in text, (needle, text)
+    cfg2 = load_config(CFG)
+    cfg2.benchmark_type, cfg2.test_name = "nccl_allscatter", "allscatter"
+    assert any("no benchmark named 'allscatter'" in p for p in cfg2.problems())
+    cfg3 = load_config(CFG)
+    cfg3.benchmark_type, cfg3.app_command, cfg3.gendata_targets = "app_gendata", "", ""
+    assert len(cfg3.problems()) == 2
+    # the command line refuses such a configuration with the list
+    bad = tmp_path / "cfg"
+    import shutil
+
+    shutil.copytree(CFG, bad)
+    p = bad / "job_config.jsonc"
+    p.write_text(p.read_text().replace('"local"', '"pbs"', 1))
+    r = subprocess.run([sys.executable, "-m", "ccbench_b200.cli", "--config-dir", str(bad), "gen-script"], capture_output=True, text=True,
+                       cwd=ROOT)
+    if '"pbs"' in p.read_text():   # the shipped file selects the launcher by that literal
+        assert r.returncode == 2 and "job_choice 'pbs'" in r.stderr, r.stderr
