@@ -36,3 +36,22 @@ def test_residual_roundtrip_and_refusals(tmp_path):
     torch.save({"x": 1}, str(tmp_path / "other.pt"))
     with pytest.raises(ValueError):
         state.load_residual(str(tmp_path / "other.pt"), rank=0, nranks=1, count=1, codec="int8")
+
+
+def test_report_tables(tmp_path, capsys):
+    from ccbench_b200.bench import report
+
+    csv = tmp_path / "s.csv"
+    csv.write_text("msg_size,nranks,dtype,algo,codec,time_us,algbw,busbw,ref_bw,ratio,rel_l2\n"
+                   "1048576,8,bf16,auto,int8,60.0,17.3,30.3,34.6,1.9,4e-3\n"
+                   "1048576,8,bf16,ring,int8,130.0,8.0,14.1,16.1,1.9,1e-2\n"
+                   "1048576,8,bf16,nccl,none,57.0,18.4,32.2,36.8,1.0,3e-3\n"
+                   "msg_size,nranks,dtype,algo,codec,time_us,algbw,busbw,ref_bw,ratio,rel_l2\n"
+                   "268435456,8,bf16,auto,int8,494.0,543,951,1087,1.9,7e-3\n"
+                   "268435456,8,bf16,nccl,none,709.0,378,663,757,1.0,2e-3\n")
+    assert report.main([str(csv), "--value", "busbw"]) == 0
+    out = capsys.readouterr().out
+    assert "### 8 ranks, bf16, busbw" in out
+    assert "| 1 MiB | 30.3 | 14.1 | 32.2 | 0.95 x |" in out
+    assert "| 256 MiB | 951.0 | – | 663.0 | 1.44 x |" in out
+    assert report.human(8) == "8 B" and report.human(3 << 30) == "3 GiB"
