@@ -199,6 +199,17 @@ def main():
 
     factor = 2 * (world - 1) / world if world > 1 else 1.0
     algbw = args.bytes / (ms_per_step * 1e-3) / 1e9
+    # roofline of the fused kernel: the wire bytes one GPU must push over NVLink at the
+    # 770 GB/s measured for a peer copy on this pool (one rank: input + output at the measured
+    # 6553 GB/s copy bandwidth)
+    from ccbench_b200.comm import wire_bytes as _wire_bytes
+
+    if world > 1:
+        bound_ms = factor * _wire_bytes(args.codec, dtype, count) / 770e9 * 1e3
+        roofline = {"bound": "nvlink", "gbs": 770, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step}
+    else:
+        bound_ms = 2 * args.bytes / 6553e9 * 1e3
+        roofline = {"bound": "hbm", "gbs": 6553, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step}
     if rank == 0:
         line = {
             "metric": "compressed_allreduce_busbw",
@@ -218,7 +229,7 @@ def main():
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},
             "algbw": algbw, "ref_definition_bw": 2 * algbw, "compression_ratio": wire_ratio(args.codec, dtype),
             "rel_l2_error": rel_l2, "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "e2e": e2e, "gpu_launches": launches, "host_numa_binding": numa,
+            "e2e": e2e, "gpu_launches": launches, "host_numa_binding": numa, "roofline": roofline,
         }
         print(json.dumps(line), flush=True)
     comm.close()
