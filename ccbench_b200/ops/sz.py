@@ -285,3 +285,31 @@ def restate(field: np.ndarray, eb: float):
     tile_bytes = 64 + 4 * w.sum(axis=(-1, -2))
     tile_bytes = (tile_bytes + 15) // 16 * 16
     return recon, int(tile_bytes.sum())
+
+
+def selfcheck(n: int = 48, eb_rel: float = 1e-3, device: str = "cuda") -> dict:
+    """Cross-check of the two implementations of the format on a small field: what the GPU
+    packs, the NumPy decoder must read back to the GPU decoder's values, and what the NumPy
+    encoder packs, the GPU must decode to the NumPy decoder's values.
+    `python -m ccbench_b200.ops.sz` prints the outcome."""
+    from ..models.workloads import smooth_field
+
+    f = smooth_field(n, seed=3, device=device)[:, : n - 5, : n - 3].contiguous()
+    eb = eb_rel * (f.max() - f.min()).item()
+    buf, _ = compress(f, eb)
+    gpu = decompress(buf, f.shape, eb).cpu().numpy()
+    blob = to_container(buf, f.shape, eb).cpu().numpy()
+    cpu_from_gpu = decode_cpu(blob)
+    blob_cpu = encode_cpu(f.cpu().numpy(), eb)
+    buf2, shape2, eb2 = from_container(torch.from_numpy(blob_cpu).to(device))
+    gpu_from_cpu = decompress(buf2, shape2, eb2).cpu().numpy()
+    return {"gpu_pack_cpu_unpack": bool(np.array_equal(cpu_from_gpu, gpu)),
+            "cpu_pack_gpu_unpack": bool(np.array_equal(gpu_from_cpu, decode_cpu(blob_cpu))),
+            "same_bytes": bool(blob.size == blob_cpu.size and np.array_equal(blob, blob_cpu)),
+            "bytes": int(blob.size)}
+
+
+if __name__ == "__main__":
+    import json
+
+    print(json.dumps(selfcheck()))
