@@ -378,6 +378,24 @@ int ncclAllToAll(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype,
     return f ? f(sendbuf, sendcount, sendtype, recvbuf, recvcount, recvtype, comm, stream) : 1;
 }
 
+/* NCCL 2.28 added its own all-to-all under a different spelling and signature (count per
+ * peer, one type): same fused path. The prototype is written out because older nccl.h
+ * headers, which this file must also compile against, do not have it. */
+typedef ncclResult_t (*fn_a2a_228)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+ncclResult_t ncclAlltoAll(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
+                          cudaStream_t stream) {
+    ccb_comm *c = fused_comm(comm, datatype, count * 2, stream, NULL, NULL);
+    if (c) {
+        const void *s[1] = {sendbuff};
+        void *r[1] = {recvbuff};
+        int rc = ccb_all_to_all(c, s, r, count, dtype_of(datatype), cfg.move_codec, stream);
+        if (rc != CCB_ERR_UNSUPPORTED && rc != CCB_ERR_CAPACITY) return to_nccl(rc);
+    }
+    static fn_a2a_228 real;
+    if (!real) real = (fn_a2a_228)dlsym(RTLD_NEXT, "ncclAlltoAll");
+    return real ? real(sendbuff, recvbuff, count, datatype, comm, stream) : ncclInvalidUsage;
+}
+
 int ncclScatter(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
                 ncclDataType_t recvtype, int root, ncclComm_t comm, cudaStream_t stream) {
     ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, sendcount * 2, stream, NULL, NULL) : NULL;
