@@ -1,0 +1,1 @@
+"""Benchmarks: size sweep, configurations 1-5, phase timelines, profiler cases, report tables."""

@@ -1,0 +1,1 @@
+"""Synthetic workloads: the data distributions and shapes the benchmarks run on."""

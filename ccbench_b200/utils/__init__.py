@@ -1,0 +1,1 @@
+"""Host utilities: clock sampling, NUMA binding, environment description, persistent state."""
