@@ -23,6 +23,10 @@ def build(verbose: bool = False) -> None:
     ]:
         if src.exists():
             nb.cc(libs / name, [src], shared=True, libs=extra, verbose=verbose)
+    # loader of the library under the preload chain (base_ncclXxx)
+    base = root / "csrc/core/base_impl.c"
+    if base.exists():
+        nb.cc(libs / "libccb_base_impl.so", [base], shared=True, libs=["-ldl"], verbose=verbose)
     # perf wrapper for the NCCL path: plain cc, no CUDA or NCCL headers
     perf_src = [root / "userconfig/wrapper_code_examples/perf/perfnccl/perfnccl.c",
                 root / "csrc/wrappers/perf_helper_nccl.c", root / "csrc/core/perf.c"]
