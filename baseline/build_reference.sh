@@ -5,12 +5,13 @@
 # script is the offline install used by `bench.py --impl reference`.
 #
 #   usage: baseline/build_reference.sh [/path/to/reference/source]
+#   (or the CCB_REFERENCE_DIR environment variable; the argument wins)
 set -euo pipefail
 HERE="$(cd "$(dirname "$0")" && pwd)"
-SRC="${1:-/root/reference}"
+SRC="${1:-${CCB_REFERENCE_DIR:-}}"
 DST="$HERE/_ref/CC-Bench"
 if [ ! -d "$DST" ]; then
-    [ -d "$SRC" ] || { echo "reference source $SRC not found"; exit 1; }
+    [ -n "$SRC" ] && [ -d "$SRC" ] || { echo "reference source not found: pass its path or set CCB_REFERENCE_DIR"; exit 1; }
     mkdir -p "$HERE/_ref"
     cp -r "$SRC" "$DST"
     chmod -R u+w "$DST"

@@ -245,7 +245,7 @@ def generate(cfg: BenchConfig, bench_dir: str | os.PathLike, check_launcher: boo
             where = cfg.output_bin_path or "gendata"
             where = where if os.path.isabs(where) else "$BENCH_DIR/" + where
             L(f'export PERF_GENDATA_OUTPUT_DIR="${{PERF_GENDATA_OUTPUT_DIR:-{where}}}"')
-            L('export PERF_GENDATA_DONE_DIR="$BENCH_DIR/daemon_signals"')
+            L('export PERF_GENDATA_DONE_DIR="${PERF_GENDATA_DONE_DIR:-$BENCH_DIR/daemon_signals}"')
             L('mkdir -p "$PERF_GENDATA_OUTPUT_DIR"')
         L("PHASE2_DAEMON_PIDS=()")
         _daemon_start(L, cfg.phase2_daemons, "PHASE2_DAEMON_PIDS", cfg)

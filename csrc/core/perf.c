@@ -227,6 +227,14 @@ int perf_gendata_load_targets(perf_state_t *s) {
         if (s->gc_occ_cnt[e] > 0) s->gc_num_entries++;
     }
     free(copy);
+    if (s->gc_num_entries > 0) {
+        /* A marker left by an earlier capture run would let the peers leave while this rank is
+         * still inside a collective: every rank removes its own before its first call. */
+        const char *done_dir = getenv("PERF_GENDATA_DONE_DIR");
+        char mark[1024];
+        snprintf(mark, sizeof(mark), "%s/gendata_done_%d", (done_dir && *done_dir) ? done_dir : "daemon_signals", s->gc_rank);
+        unlink(mark);
+    }
     return s->gc_num_entries;
 }
 

@@ -68,7 +68,7 @@ def test_capture_run_dumps_buffers_that_feed_a_later_run(tmp_path):
     cfg.perf = dataclasses.replace(cfg.perf, mode=1, library_paths=["bin/libs/libperfmpi.so"])
     cfg.env = {"CCB_MINIMPI_JOB": f"cap{os.getpid()}"}
     script = runscript.write(cfg, ROOT, out_dir=tmp_path)
-    env = dict(os.environ, PERF_OUTPUT_DIR=str(tmp_path / "perf_files"))
+    env = dict(os.environ, PERF_OUTPUT_DIR=str(tmp_path / "perf_files"), PERF_GENDATA_DONE_DIR=str(tmp_path / "done"))
     env.pop("LD_PRELOAD", None)
     env.pop("PERF_GENDATA_OUTPUT_DIR", None)
     r = subprocess.run(["bash", str(script)], capture_output=True, text=True, timeout=600, env=env)
