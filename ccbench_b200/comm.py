@@ -109,6 +109,14 @@ class Communicator:
         L.ccb_comm_set_waves.argtypes = [ctypes.c_void_p, ctypes.c_int]
         _check(L.ccb_comm_set_waves(self._h, waves))
 
+    def set_pipeline(self, mode: int = 1, link_warps: int = 0, multicast: bool = True) -> None:
+        """The warp-specialised pipelined two-shot kernel: mode 0 never, 1 when the message is
+        large enough, 2 always; link_warps of a CTA's 15 data warps store over NVLink (0 keeps
+        the current value); multicast lets phase 2 store once through an NVLS mapping."""
+        L = lib()
+        L.ccb_comm_set_pipeline.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+        _check(L.ccb_comm_set_pipeline(self._h, mode, link_warps, 1 if multicast else 0))
+
     def set_trace(self, on: bool) -> None:
         L = lib()
         L.ccb_comm_set_trace.argtypes = [ctypes.c_void_p, ctypes.c_int]

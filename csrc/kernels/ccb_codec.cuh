@@ -77,6 +77,11 @@ struct CodecNone {
 #pragma unroll
     for (int k = 0; k < kQ; ++k) pk.q[k] = ldg_cg(slot + wire_off(idx, k));
   }
+  // `slot` is an address inside an NVLS multicast mapping: one store reaches every arena.
+  static __device__ __forceinline__ void store_mc(char* slot, size_t pad, size_t idx, const Packet& pk) {
+#pragma unroll
+    for (int k = 0; k < kQ; ++k) mc_st16(slot + wire_off(idx, k), pk.q[k]);
+  }
 };
 
 __device__ __forceinline__ float absmax16(const float (&v)[16]) {
@@ -124,6 +129,10 @@ struct CodecInt8 {
     pk.q = ldg_cg(slot + idx);
     pk.scale = __uint_as_float(ldg_cg_u32(slot + pad + (idx / G) * 4));
   }
+  static __device__ __forceinline__ void store_mc(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    mc_st16(slot + idx, pk.q);
+    if ((threadIdx.x & (kLanes - 1)) == 0) mc_st4(slot + pad + (idx / G) * 4, __float_as_uint(pk.scale));
+  }
 };
 
 // Symmetric 4-bit integers, fp32 scale = absmax/7 per 128 values: 0.53 bytes per value,
@@ -159,6 +168,10 @@ struct CodecInt4 {
   static __device__ __forceinline__ void load(const char* slot, size_t pad, size_t idx, Packet& pk) {
     pk.q = ldg_cg8(slot + idx / 2);
     pk.scale = __uint_as_float(ldg_cg_u32(slot + pad / 2 + (idx / kGroup) * 4));
+  }
+  static __device__ __forceinline__ void store_mc(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    mc_st8(slot + idx / 2, pk.q);
+    if ((threadIdx.x & (kLanes - 1)) == 0) mc_st4(slot + pad / 2 + (idx / kGroup) * 4, __float_as_uint(pk.scale));
   }
 };
 
@@ -209,6 +222,18 @@ struct CodecFp8 {
     uint32_t e;
     asm volatile("ld.global.cg.u8 %0, [%1];" : "=r"(e) : "l"(slot + pad + idx / 32));
     pk.e = e & 0xffu;
+  }
+  // Multicast stores have no byte form: the four scale bytes of eight neighbouring lanes
+  // travel as one word. Warp-collective (every lane of the warp must call it, with the
+  // 32 lanes on 512 consecutive elements).
+  static __device__ __forceinline__ void store_mc(char* slot, size_t pad, size_t idx, const Packet& pk) {
+    mc_st16(slot + idx, pk.q);
+    const int lane = threadIdx.x & 31;
+    uint32_t w = pk.e;
+    w |= __shfl_down_sync(0xffffffffu, pk.e, 2) << 8;
+    w |= __shfl_down_sync(0xffffffffu, pk.e, 4) << 16;
+    w |= __shfl_down_sync(0xffffffffu, pk.e, 6) << 24;
+    if ((lane & 7) == 0) mc_st4(slot + pad + idx / 32, w);
   }
 };
 

@@ -167,6 +167,18 @@ __device__ __forceinline__ void stg(void* p, uint4 v) {
   asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Stores to an NVLink multicast (NVLS) address: the switch writes the value into the
+// memory of every GPU bound to the multicast object; the sender's link carries it once.
+__device__ __forceinline__ void mc_st16(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void mc_st8(void* p, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void mc_st4(void* p, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // Load the 16 elements [idx, idx+16) of `base` as fp32; elements at or beyond
 // `limit` read as 0. Vector path when the lane is fully inside and 16-byte aligned.
 template <class T>

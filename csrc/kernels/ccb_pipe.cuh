@@ -1,0 +1,398 @@
+// Warp-specialised, software-pipelined two-shot AllReduce / ReduceScatter for large
+// messages: the same wire protocol as reduce_kernel (ccb_reduce.cuh), but the three
+// phases of a wave run on different warps of a CTA, so the NVLink-bound phases and
+// the HBM-bound decode overlap instead of alternating.
+//
+//   link warps    P1(w+1): quantise, store lanes into the owners' arenas     (NVLink out)
+//                 P2(w)  : reduce own shard, requantise once, store to peers (NVLink out;
+//                          ONE multimem.st per lane where the arenas have an NVLS mapping)
+//   decode warps  P3(w)  : decode the reduced shards into recv               (HBM only)
+//                 (ReduceScatter: they run the reduction P2 instead; there is no P3)
+//   signal warp   owns every fence.acq_rel.sys + flag store: the link warps hand a phase
+//                 over through a shared-memory counter and go on storing, so the
+//                 20 us a system fence costs under store load is off their path.
+//
+// Flag row 2w carries phase 1 of wave w, row 2w+1 phase 2, as in reduce_kernel. Inside a
+// role group the first warp polls the peers' flags and publishes "wave w is ready" in
+// shared memory; the other warps of the group spin there, not on global memory.
+//
+// The reference does this job as 2(n-1) host-driven hops of quantize kernel, ncclSend,
+// ncclRecv, dequantize kernel, cudaStreamSynchronize, reduce kernel
+// (userconfig/wrapper_code_examples/communication/plain_nccl_compress/
+// plain_nccl_compress.cu:682-773 AllReduce, :970-1076 ReduceScatter).
+#pragma once
+#include "ccb_reduce.cuh"
+
+namespace ccb {
+
+constexpr int kPipeChunkShift = 3;                    // a CTA owns runs of 8 units (4096 elements)
+constexpr int kPipeChunkUnits = 1 << kPipeChunkShift;
+
+struct PipeShared {
+  unsigned int p1_done;    // link-warp arrivals after phase 1, summed over the waves
+  unsigned int p2_done;    // the same after phase 2
+  unsigned int p1_ready;   // waves whose phase-1 flags from all peers have been seen
+  unsigned int p2_ready;   // the same for phase 2
+  int fail;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_cta_shared(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_cta_shared_add(unsigned int* p, unsigned int v) {
+  asm volatile("red.release.cta.shared.add.u32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_volatile_shared_int(const int* p) {
+  int v;
+  asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"((unsigned)__cvta_generic_to_shared(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_shared_int(int* p, int v) {
+  asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"((unsigned)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+
+// Lane 0 of the calling warp waits until the shared counter reaches `target`; the whole
+// warp learns the verdict. Gives up when another warp of the CTA failed, when the abort
+// word carries this epoch, or after the communicator's time limit; never traps.
+__device__ __forceinline__ bool warp_wait_counter(const unsigned int* ctr, unsigned int target, PipeShared& sh,
+                                                  const CommDev& c, char* my_arena, int where) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) {
+    uint64_t t0 = 0;
+    uint32_t polls = 0;
+    while ((int)(ld_acquire_cta_shared(ctr) - target) < 0) {
+      if (ld_volatile_shared_int(&sh.fail)) { ok = 0; break; }
+      if ((++polls & 0x3f) == 0) {
+        if (t0 == 0) t0 = globaltimer_ns();
+        const bool aborted = ld_relaxed_sys(ctrl_ptr(my_arena, CCB_CTRL_ABORT)) == c.epoch;
+        const bool late = (globaltimer_ns() - t0) > c.timeout_ns || polls > (1u << 30);
+        if (aborted || late) {
+          if (c.status) {
+            atomicOr(c.status + CCB_STATUS_FLAGS, aborted ? CCB_ST_ABORTED : CCB_ST_TIMEOUT);
+            if (!aborted && atomicCAS(c.status + CCB_STATUS_WHERE, 0u, (uint32_t)where | 0x80000000u) == 0u) {
+              c.status[CCB_STATUS_EPOCH] = c.epoch;
+              c.status[CCB_STATUS_SEEN] = ld_acquire_cta_shared(ctr);
+            }
+          }
+          st_volatile_shared_int(&sh.fail, 1);
+          if (!aborted) broadcast_abort(c, c.epoch);
+          ok = 0;
+          break;
+        }
+      }
+      __nanosleep(64);
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// The polling warp of a role group: lanes < n wait for flag (row, source = lane, this CTA).
+__device__ __forceinline__ bool warp_wait_sources(const CommDev& c, char* my_arena, int row, int self, PipeShared& sh,
+                                                  int where) {
+  const int lane = threadIdx.x & 31;
+  int ok = 1;
+  if (lane < c.nranks && lane != self) {
+    const uint32_t* flag = flag_ptr(my_arena, row, lane, blockIdx.x);
+    uint64_t t0 = 0;
+    uint32_t polls = 0;
+    for (;;) {
+      const uint32_t v = ld_acquire_sys(flag);
+      if ((int32_t)(v - c.epoch) >= 0) break;
+      if ((++polls & 0x3f) == 0) {
+        if (t0 == 0) t0 = globaltimer_ns();
+        const bool aborted = ld_relaxed_sys(ctrl_ptr(my_arena, CCB_CTRL_ABORT)) == c.epoch || ld_volatile_shared_int(&sh.fail);
+        const bool late = (globaltimer_ns() - t0) > c.timeout_ns || polls > (1u << 30);
+        if (aborted || late) {
+          if (c.status) {
+            atomicOr(c.status + CCB_STATUS_FLAGS, aborted ? CCB_ST_ABORTED : CCB_ST_TIMEOUT);
+            if (!aborted && atomicCAS(c.status + CCB_STATUS_WHERE, 0u, (uint32_t)(where | (lane << 8)) | 0x80000000u) == 0u) {
+              c.status[CCB_STATUS_EPOCH] = c.epoch;
+              c.status[CCB_STATUS_SEEN] = v;
+            }
+          }
+          ok = 0;
+          break;
+        }
+      }
+      __nanosleep(100);
+    }
+  }
+  const bool all = __all_sync(0xffffffffu, ok);
+  if (!all && lane == 0) {
+    st_volatile_shared_int(&sh.fail, 1);
+    broadcast_abort(c, c.epoch);
+  }
+  return all;
+}
+
+// Group-wide wait for "the flags of `row` have arrived" (wave number `w`): the group's
+// first warp polls global memory and publishes w + 1 in `ready`; the others wait there.
+__device__ __forceinline__ bool group_wait(bool leader, unsigned int* ready, int w, int row, const CommDev& c,
+                                           char* my_arena, int self, PipeShared& sh, int where) {
+  if (leader) {
+    const bool ok = warp_wait_sources(c, my_arena, row, self, sh, where);
+    if (ok && (threadIdx.x & 31) == 0) st_release_cta_shared(ready, (unsigned int)(w + 1));
+    return ok;
+  }
+  return warp_wait_counter(ready, (unsigned int)(w + 1), sh, c, my_arena, where | 0x8000);
+}
+
+// A finished phase handed to the signal warp: every lane's stores are ordered before
+// lane 0's release by the warp barrier.
+__device__ __forceinline__ void warp_arrive(unsigned int* ctr) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) red_release_cta_shared_add(ctr, 1u);
+}
+
+template <class T, class C>
+__global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant__ ReduceArgs a) {
+  __shared__ PipeShared sh;
+  const CommDev& c = a.c;
+  const int lr = blockIdx.y, r = a.rank0 + lr, n = c.nranks;
+  const size_t b = blockIdx.x, G = gridDim.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int L = a.link_warps, D = kWarps - 1 - L;  // warp kWarps-1 signals
+  const int W = a.waves;
+  const bool ar = (a.mode == CCB_MODE_ALLREDUCE);
+  const T* send = static_cast<const T*>(a.send[lr]);
+  T* recv = static_cast<T*>(a.recv[lr]);
+  float* ef = a.ef[lr];
+  char* my = c.arena[r];
+  const size_t half = CCB_DATA_OFFSET + (size_t)(c.epoch & 1u) * c.half_bytes;
+  const size_t area1 = half, area2 = half + (size_t)n * a.slot_bytes;
+  const size_t pad = a.shard_pad;
+  const bool use_mc = a.use_mc && c.mc_arena != nullptr;
+  const uint32_t peers = ((1u << n) - 1u) & ~(1u << r);
+  if (threadIdx.x == 0) {
+    sh.p1_done = sh.p2_done = sh.p1_ready = sh.p2_ready = 0u;
+    sh.fail = 0;
+  }
+  __syncthreads();  // the only CTA-wide barrier: the roles part ways here
+
+  auto shard_valid = [&](int s) -> size_t {
+    const size_t beg = (size_t)s * a.shard_elems;
+    if (beg >= a.count) return 0;
+    const size_t left = a.count - beg;
+    return left < a.shard_elems ? left : a.shard_elems;
+  };
+  // Items (512-element units) of this CTA in wave w of a shard with `valid` elements:
+  // the CTA owns chunks b, b + G, b + 2G, ... of 8 units; the wave takes a slice of them.
+  auto wave_items = [&](size_t valid, int w, size_t& kb) -> size_t {
+    const size_t units = (valid + kWarpElems - 1) / kWarpElems;
+    const size_t nch = (units + kPipeChunkUnits - 1) >> kPipeChunkShift;
+    const size_t K = nch > b ? (nch - b + G - 1) / G : 0;
+    kb = K * (size_t)w / W;
+    return (K * (size_t)(w + 1) / W - kb) << kPipeChunkShift;
+  };
+  auto item_elem = [&](size_t kb, size_t i) -> size_t {
+    const size_t ch = b + (kb + (i >> kPipeChunkShift)) * G;
+    return ((ch << kPipeChunkShift) + (i & (kPipeChunkUnits - 1))) * kWarpElems;
+  };
+
+  // ---- phase 1 of wave w: this rank's lanes of every peer's shard, to the owner ----
+  auto phase1 = [&](int w, int gw, int gn) {
+    for (int j = 1; j < n; ++j) {
+      const int p = (r + j) % n;
+      const size_t valid = shard_valid(p);
+      const T* src = send + (size_t)p * a.shard_elems;
+      float* efs = ef ? ef + (size_t)p * a.shard_elems : nullptr;
+      char* dst = c.arena[p] + area1 + (size_t)r * a.slot_bytes;
+      size_t kb;
+      const size_t items = wave_items(valid, w, kb);
+      for (size_t i = gw; i < items; i += 2 * (size_t)gn) {
+        const size_t e0 = item_elem(kb, i);
+        const size_t i1 = i + gn;
+        const size_t e1 = i1 < items ? item_elem(kb, i1) : valid;
+        float v0[16], v1[16];
+        const bool h0 = e0 < valid, h1 = e1 < valid;
+        if (h0) load16<T>(src, e0 + lane * kLaneElems, valid, v0);
+        if (h1) load16<T>(src, e1 + lane * kLaneElems, valid, v1);
+        auto one = [&](size_t idx, float (&v)[16]) {
+          if (efs) {
+            float e[16];
+            load16f_plain(efs, idx, valid, e);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] += e[q];
+          }
+          typename C::Packet pk;
+          C::encode(v, pk);
+          C::store(dst, pad, idx, pk);
+          if (efs) {
+            float d[16];
+            C::decode(pk, d);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) d[q] = v[q] - d[q];
+            store16f_plain(efs, idx, valid, d);
+          }
+        };
+        if (h0) one(e0 + lane * kLaneElems, v0);
+        if (h1) one(e1 + lane * kLaneElems, v1);
+      }
+    }
+  };
+
+  // ---- phase 2 of wave w: reduce the own shard; AllReduce requantises and sends it ----
+  auto phase2 = [&](int w, int gw, int gn) {
+    const size_t valid = shard_valid(r);
+    const T* src = send + (size_t)r * a.shard_elems;
+    float* efs = (ef && ar) ? ef + (size_t)r * a.shard_elems : nullptr;
+    T* out = ar ? recv + (size_t)r * a.shard_elems : recv;
+    size_t kb;
+    const size_t items = wave_items(valid, w, kb);
+    for (size_t i = gw; i < items; i += gn) {
+      const size_t e0 = item_elem(kb, i);
+      if (e0 >= valid) continue;
+      const size_t idx = e0 + lane * kLaneElems;
+      float acc[16];
+      load16<T>(src, idx, valid, acc);
+      // The sources' packets are fetched in batches before any is decoded, so that a lane
+      // has several loads in flight instead of one round trip to memory per source.
+      constexpr int kBatch = sizeof(typename C::Packet) <= 32 ? 4 : 2;
+      for (int q0 = 0; q0 < n; q0 += kBatch) {
+        typename C::Packet in[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k)
+          if (q0 + k < n && q0 + k != r) C::load(my + area1 + (size_t)(q0 + k) * a.slot_bytes, pad, idx, in[k]);
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          if (q0 + k < n && q0 + k != r) {
+            float d[16];
+            C::decode(in[k], d);
+#pragma unroll
+            for (int e = 0; e < 16; ++e) acc[e] = apply_op(a.op, acc[e], d[e]);
+          }
+        }
+      }
+      if (!ar) {  // ReduceScatter delivers the fp32 sum without a second quantisation
+        store16<T>(out, idx, valid, acc);
+        continue;
+      }
+      if (efs) {
+        float e[16];
+        load16f_plain(efs, idx, valid, e);
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc[k] += e[k];
+      }
+      typename C::Packet pk;
+      C::encode(acc, pk);
+      if (use_mc) {
+        C::store_mc(c.mc_arena + area2 + (size_t)r * a.slot_bytes, pad, idx, pk);
+      } else {
+        for (int j = 1; j < n; ++j) C::store(c.arena[(r + j) % n] + area2 + (size_t)r * a.slot_bytes, pad, idx, pk);
+      }
+      float d[16];
+      C::decode(pk, d);
+      if (efs) {
+        float e[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) e[k] = acc[k] - d[k];
+        store16f_plain(efs, idx, valid, e);
+      }
+      store16<T>(out, idx, valid, d);
+    }
+  };
+
+  // ---- phase 3 of wave w: decode the peers' reduced shards ----
+  auto phase3 = [&](int w, int gw, int gn) {
+    for (int j = 1; j < n; ++j) {
+      const int q = (r + j) % n;
+      const size_t valid = shard_valid(q);
+      const char* slot = my + area2 + (size_t)q * a.slot_bytes;
+      T* out = recv + (size_t)q * a.shard_elems;
+      size_t kb;
+      const size_t items = wave_items(valid, w, kb);
+      for (size_t i = gw; i < items; i += 2 * (size_t)gn) {
+        const size_t e0 = item_elem(kb, i);
+        const size_t i1 = i + gn;
+        const size_t e1 = i1 < items ? item_elem(kb, i1) : valid;
+        const bool h0 = e0 < valid, h1 = e1 < valid;
+        typename C::Packet p0, p1;
+        if (h0) C::load(slot, pad, e0 + lane * kLaneElems, p0);
+        if (h1) C::load(slot, pad, e1 + lane * kLaneElems, p1);
+        float d[16];
+        if (h0) {
+          C::decode(p0, d);
+          store16<T>(out, e0 + lane * kLaneElems, valid, d);
+        }
+        if (h1) {
+          C::decode(p1, d);
+          store16<T>(out, e1 + lane * kLaneElems, valid, d);
+        }
+      }
+    }
+  };
+
+  const bool tr = c.trace != nullptr && lane == 0;
+  auto mark = [&](int k) {
+    if (tr) c.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * CCB_TRACE_SLOTS + k] = globaltimer_ns();
+  };
+
+  if (warp < L) {
+    // ------------------------------------------------------------ link warps ----
+    const bool leader = (warp == 0);
+    if (leader) mark(0);
+    phase1(0, warp, L);
+    warp_arrive(&sh.p1_done);
+    if (leader) mark(1);
+    if (ar) {
+      for (int w = 0; w < W; ++w) {
+        if (w + 1 < W) {
+          phase1(w + 1, warp, L);
+          warp_arrive(&sh.p1_done);
+        }
+        if (!group_wait(leader, &sh.p1_ready, w, 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
+        phase2(w, warp, L);
+        warp_arrive(&sh.p2_done);
+        if (leader && w == 0) mark(2);
+      }
+      if (leader) mark(3);
+    } else {
+      for (int w = 1; w < W; ++w) {
+        phase1(w, warp, L);
+        warp_arrive(&sh.p1_done);
+      }
+      if (leader) mark(3);
+    }
+  } else if (warp < L + D) {
+    // ---------------------------------------------------------- decode warps ----
+    const int gw = warp - L;
+    const bool leader = (gw == 0);
+    for (int w = 0; w < W; ++w) {
+      if (ar) {
+        if (!group_wait(leader, &sh.p2_ready, w, 2 * w + 1, c, my, r, sh, 0x20 | (w << 16))) return;
+        phase3(w, gw, D);
+      } else {
+        if (!group_wait(leader, &sh.p1_ready, w, 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
+        phase2(w, gw, D);
+      }
+      if (leader && w == 0) mark(5);
+    }
+    if (leader) mark(4);
+  } else {
+    // ----------------------------------------------------------- signal warp ----
+    // Events in the order the link warps produce them: P1(0), then per wave P1(w+1), P2(w).
+    auto publish = [&](int row) {
+      if (lane == 0) signal_peers(c, peers, row, r, (int)b);
+      __syncwarp();
+    };
+    if (!warp_wait_counter(&sh.p1_done, (unsigned)L, sh, c, my, 0xA0)) return;
+    publish(0);
+    for (int w = 0; w < W; ++w) {
+      if (w + 1 < W) {
+        if (!warp_wait_counter(&sh.p1_done, (unsigned)(L * (w + 2)), sh, c, my, 0xA0 | ((w + 1) << 16))) return;
+        publish(2 * (w + 1));
+      }
+      if (ar) {
+        if (!warp_wait_counter(&sh.p2_done, (unsigned)(L * (w + 1)), sh, c, my, 0xB0 | (w << 16))) return;
+        publish(2 * w + 1);
+      }
+    }
+  }
+}
+
+}  // namespace ccb

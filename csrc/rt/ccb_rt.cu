@@ -20,6 +20,7 @@
 
 #include "../kernels/ccb_exchange.cuh"
 #include "../kernels/ccb_nvls.cuh"
+#include "../kernels/ccb_pipe.cuh"
 #include "../kernels/ccb_reduce.cuh"
 #include "../kernels/ccb_ring.cuh"
 #include "ccb/ccb.h"
@@ -143,6 +144,10 @@ struct ccb_comm {
   int num_sms = 0;
   int max_ctas = 0;
   int waves = 0;  // 0 = choose per call
+  int pipe_mode = 1;        // 0 = never use the pipelined two-shot kernel, 1 = when large enough, 2 = always
+  int pipe_min_chunks = 4;  // chunks (4096 elements) per CTA from which it is used
+  int pipe_link_warps = 10; // of the 15 data warps, how many store over NVLink
+  int pipe_mc = 1;          // phase 2 through the NVLS multicast mapping when there is one
   unsigned long long* trace = nullptr;  // device buffer, CCB_MAX_CTAS * nlocal * CCB_TRACE_SLOTS
   bool dead = false;
   // ownership
@@ -173,6 +178,12 @@ static int finish_common(ccb_comm* c) {
   c->timeout_ns = env_u64("CCB_TIMEOUT_MS", 10000) * 1000000ull;
   c->max_ctas = (int)env_u64("CCB_MAX_CTAS", 0);
   c->waves = (int)env_u64("CCB_WAVES", 0);
+  c->pipe_mode = (int)env_u64("CCB_PIPE", 1);
+  c->pipe_min_chunks = (int)env_u64("CCB_PIPE_MIN_CHUNKS", 4);
+  c->pipe_link_warps = (int)env_u64("CCB_PIPE_LINK_WARPS", 10);
+  if (c->pipe_link_warps < 1) c->pipe_link_warps = 1;
+  if (c->pipe_link_warps > kWarps - 2) c->pipe_link_warps = kWarps - 2;
+  c->pipe_mc = (int)env_u64("CCB_PIPE_MC", 1);
   RT_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), CCB_STATUS_WORDS * 4, cudaHostAllocMapped));
   memset(c->status_host, 0, CCB_STATUS_WORDS * 4);
   RT_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
@@ -578,6 +589,15 @@ extern "C" int ccb_comm_set_waves(ccb_comm* c, int waves) {
   c->waves = waves;
   return CCB_OK;
 }
+/* Pipelined two-shot kernel: mode 0 never / 1 when the message is large enough / 2 always;
+ * link_warps in [1, 14] (0 keeps the current value); mc != 0 lets phase 2 use the NVLS mapping. */
+extern "C" int ccb_comm_set_pipeline(ccb_comm* c, int mode, int link_warps, int mc) {
+  if (!c || mode < 0 || mode > 2 || link_warps < 0 || link_warps > kWarps - 2) return CCB_ERR_ARG;
+  c->pipe_mode = mode;
+  if (link_warps > 0) c->pipe_link_warps = link_warps;
+  c->pipe_mc = mc ? 1 : 0;
+  return CCB_OK;
+}
 extern "C" int ccb_comm_status(ccb_comm* c, uint32_t* words) {
   if (!c) return CCB_ERR_ARG;
   if (words) memcpy(words, c->status_host, CCB_STATUS_WORDS * 4);
@@ -620,6 +640,9 @@ static const void* reduce_fn(int dtype, int codec, int shape) {
   if (shape == kOneShot) return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&reduce_kernel<TT, CC, kOneShot>)));
   return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&reduce_kernel<TT, CC, kTwoShot>)));
 }
+static const void* pipe_fn(int dtype, int codec) {
+  return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&pipe_kernel<TT, CC>)));
+}
 static const void* exchange_fn(int dtype, int codec) {
   return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&exchange_kernel<TT, CC>)));
 }
@@ -654,6 +677,25 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
     set_error("unsupported dtype %d / codec %d", dtype, codec);
     return CCB_ERR_UNSUPPORTED;
   }
+  // Large two-shot AllReduce / ReduceScatter calls go to the warp-specialised pipelined
+  // kernel: it needs a few chunks (8 units of 512 elements) per CTA and wave to pay.
+  int pipe_waves = 0, pipe_ctas = 0;
+  if (shape == kTwoShot && mode != CCB_MODE_REDUCE && c->nranks > 1 && c->pipe_mode != 0) {
+    const void* pfn = pipe_fn(dtype, codec);
+    const int cap = grid_cap(c, pfn);
+    const size_t per = shard_elems < count ? shard_elems : count;
+    const size_t chunks = (per + (size_t)kWarpElems * kPipeChunkUnits - 1) / ((size_t)kWarpElems * kPipeChunkUnits);
+    const size_t ctas = chunks < (size_t)cap ? chunks : (size_t)cap;
+    const size_t per_cta = ctas ? chunks / ctas : 0;
+    if (per_cta >= (size_t)c->pipe_min_chunks || c->pipe_mode == 2) {
+      int w = c->waves > 0 ? c->waves : (int)(per_cta / 2);
+      if (w > CCB_MAX_SLOTS / 2) w = CCB_MAX_SLOTS / 2;
+      if (w < 1) w = 1;
+      pipe_waves = w;
+      pipe_ctas = (int)(ctas ? ctas : 1);
+      fn = pfn;
+    }
+  }
   ReduceArgs a;
   memset(&a, 0, sizeof(a));
   a.c = comm_dev(c, next_epoch(c));
@@ -672,13 +714,18 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
   a.op = op;
   a.root = root;
   a.mode = mode;
+  if (pipe_waves) {
+    a.waves = pipe_waves;
+    a.tile_warps = kWarps;
+    a.link_warps = c->pipe_link_warps;
+    a.use_mc = (c->mc_arena && c->nlocal == 1 && c->pipe_mc) ? 1 : 0;
+    return launch(c, fn, pipe_ctas, &a, stream);
+  }
   const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count, &a.tile_warps);
-  // Pipeline depth: each wave should still hold a couple of tiles per CTA.
-  const size_t tiles_per_cta = ((shard_elems < count ? shard_elems : count) / ((size_t)a.tile_warps * kWarpElems)) / (size_t)ctas;
-  // Measured on B200: each extra wave costs a pipeline drain (fence + flag round trip) that
-  // outweighs the overlap it buys, so the default is one wave; the knob stays for tuning.
+  // Each extra wave of the non-specialised kernel costs a pipeline drain (fence + flag
+  // round trip) on the data warps that outweighs the overlap it buys, so it runs one wave
+  // unless asked otherwise; the pipelined kernel above is the one that overlaps phases.
   int waves = c->waves > 0 ? c->waves : 1;
-  (void)tiles_per_cta;
   if (waves > CCB_MAX_SLOTS / 2) waves = CCB_MAX_SLOTS / 2;
   a.waves = shape == kTwoShot ? waves : 1;
   return launch(c, fn, ctas, &a, stream);

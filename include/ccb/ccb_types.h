@@ -83,6 +83,8 @@ typedef struct ReduceArgs {
   int op, root, mode;
   int waves;                  /* software-pipeline depth of the two-shot shape  */
   int tile_warps;             /* warps of a CTA that carry data: tile = 512 * tile_warps */
+  int link_warps;             /* pipelined two-shot: warps that store over NVLink (the rest decode, one signals) */
+  int use_mc;                 /* pipelined two-shot: phase 2 stores once to the NVLS multicast address */
 } ReduceArgs;
 enum { CCB_MODE_ALLREDUCE = 0, CCB_MODE_REDUCESCATTER = 1, CCB_MODE_REDUCE = 2 };
 
