@@ -50,6 +50,14 @@ static int setup_device(int dev, DeviceSlot** out) {
         return CCB_ERR_CUDA;
       }
     }
+    // cudaMemset is asynchronous to the host and runs on the legacy stream: a kernel
+    // launched right after on a non-blocking stream would not be ordered behind it, and a
+    // zero landing on a flag that was just set would make a wait run out. Wait for it.
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+      set_error("clearing the flag words failed: %s", cudaGetErrorString(e));
+      return CCB_ERR_CUDA;
+    }
     e = cudaDeviceGetAttribute(&s.num_sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess || s.num_sms < 1) {
       set_error("cannot read the SM count: %s", cudaGetErrorString(e));
@@ -80,6 +88,13 @@ static const void* twoshot_fn(int dtype, int codec) {
   return nullptr;
 }
 
+// Status words of the calls on this device: spare control words of rank 0's part of the
+// array (the kernels use words 0 and 64..72 of that region).
+constexpr int kStatusCtrlWord = 128;
+static uint32_t* status_words(DeviceSlot* s) {
+  return reinterpret_cast<uint32_t*>(s->base + CCB_CTRL_OFFSET) + kStatusCtrlWord;
+}
+
 constexpr size_t kHalfBytes = ((CCB_NOALLOC_ARENA_BYTES - CCB_DATA_OFFSET) / 2) & ~(size_t)255;
 
 static size_t shard_for(size_t count, int n) {
@@ -100,6 +115,36 @@ extern "C" uint64_t ccb_noalloc_max_count(int nranks, int dtype, int codec) {
   size_t shard = 0;
   while (2 * (size_t)nranks * codec_slot_bytes(codec, dtype, shard + kWarpElems) <= kHalfBytes) shard += kWarpElems;
   return (uint64_t)shard * (uint64_t)nranks;
+}
+
+extern "C" int ccb_noalloc_status(uint32_t* words) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  DeviceSlot* slot = &g_slots[dev];
+  uint32_t w[CCB_STATUS_WORDS] = {};
+  {
+    std::lock_guard<std::mutex> g(g_slots_lock);
+    if (!slot->base) {  // no call was made on this device yet
+      if (words) memset(words, 0, sizeof(w));
+      return CCB_OK;
+    }
+  }
+  e = cudaMemcpy(w, status_words(slot), sizeof(w), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) {
+    set_error("reading the status words failed: %s", cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  if (words) memcpy(words, w, sizeof(w));
+  if (w[CCB_STATUS_FLAGS]) {
+    set_error("a device-side wait of an earlier ccb_all_reduce_noalloc call gave up (status 0x%x, where 0x%x)",
+              w[CCB_STATUS_FLAGS], w[CCB_STATUS_WHERE]);
+    return CCB_ERR_TIMEOUT;
+  }
+  return CCB_OK;
 }
 
 extern "C" int ccb_all_reduce_noalloc(const void* const* send, void* const* recv, int nranks, uint64_t count, int dtype,
@@ -143,7 +188,7 @@ extern "C" int ccb_all_reduce_noalloc(const void* const* send, void* const* recv
     a.recv[r] = recv[r];
   }
   a.c.mc_arena = nullptr;
-  a.c.status = nullptr;   // a wait that gives up still returns; there is no status word to report it in
+  a.c.status = status_words(slot);  // read back by ccb_noalloc_status()
   a.c.trace = nullptr;
   a.c.timeout_ns = 10ull * 1000000000ull;
   a.c.half_bytes = kHalfBytes;

@@ -1052,6 +1052,14 @@ extern "C" int ccb_test_partial_all_reduce(ccb_comm* c, const void* send, void* 
     set_error("needs a local communicator and 1 <= ranks_played < nranks");
     return CCB_ERR_ARG;
   }
+  if (!send || !recv || count == 0) {
+    set_error("send, recv and a positive count are required");
+    return CCB_ERR_ARG;
+  }
+  if (2 * (size_t)c->nranks * codec_slot_bytes(CCB_CODEC_NONE, CCB_F32, round_up((count + c->nranks - 1) / c->nranks, kWarpElems)) > c->half_bytes) {
+    set_error("arena too small for this call");
+    return CCB_ERR_CAPACITY;
+  }
   const void* fn = reinterpret_cast<const void*>(&reduce_kernel<float, CodecNone<float>, kTwoShot>);
   ReduceArgs a;
   memset(&a, 0, sizeof(a));

@@ -1,12 +1,16 @@
 /* Host-codec transport helpers for NCCL wrappers.
  *
- * Same contract as the reference (run_codes/wrappers/nccl_compress_tools.c): device
- * buffer -> host -> nccl_compress -> fixed-size wire -> device -> ncclSend of bytes,
- * and the mirror image on receive (:113-166); exchange = grouped send + receive
- * (:171-229); nccl_reduce_cpu for f32/f64/i32/i64 with sum/prod/max/min (:234-293).
- * The reference allocates and frees device and host staging on every call and
- * synchronises twice; here staging is a per-thread cache that only grows, pinned so
- * the copies are asynchronous, and a call synchronises once. */
+ * Same contract as the reference (run_codes/wrappers/nccl_compress_tools.h:33-38,
+ * nccl_compress_tools.c:113-166): `buf` is a CPU (host) buffer; it is compressed with
+ * nccl_compress into the fixed-size wire, uploaded to a device staging buffer and sent
+ * with ncclSend as bytes; the receive side mirrors it and decompresses straight into
+ * the caller's host buffer. exchange = grouped send + receive (:171-229);
+ * nccl_reduce_cpu for f32/f64/i32/i64 with sum/prod/max/min (:234-293).
+ * Beyond the reference, a DEVICE (or managed) pointer is accepted too: it is staged
+ * through pinned host memory on the way in and out (cudaPointerGetAttributes tells the
+ * two apart). The reference allocates and frees device and host staging on every call
+ * and synchronises twice; here staging is a per-thread cache that only grows, pinned
+ * so the copies are asynchronous. */
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -56,16 +60,32 @@ static int stage_reserve(stage_t *s, size_t raw, size_t wire) {
     return 0;
 }
 
-/* device data -> wire on the device (in s->dev_wire) */
+/* 1 when the CUDA runtime knows `p` as device or managed memory, 0 for host memory
+ * (pinned, registered or plain malloc). */
+static int on_device(const void *p) {
+    struct cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError(); /* older runtimes report plain host memory as an error */
+        return 0;
+    }
+    return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+/* caller's data (host, or device staged through pinned memory) -> wire on the device (in s->dev_wire) */
 static int pack(stage_t *s, const void *buf, size_t n, cudaStream_t stream) {
     const size_t wire = nccl_max_wire_size(n);
-    if (stage_reserve(s, n, wire)) return -1;
-    if (cudaMemcpyAsync(s->host_raw, buf, n, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
-    if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+    const int dev = on_device(buf);
+    if (stage_reserve(s, dev ? n : 0, wire)) return -1;
+    void *raw = (void *)buf;
+    if (dev) {
+        if (cudaMemcpyAsync(s->host_raw, buf, n, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
+        if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
+        raw = s->host_raw;
+    }
     unsigned char *w = (unsigned char *)s->host_wire;
     size_t out = wire - sizeof(uint64_t);
-    if (!compression_enabled() || nccl_compress(s->host_raw, n, w + sizeof(uint64_t), &out) != 0 || out > wire - sizeof(uint64_t)) {
-        memcpy(w + sizeof(uint64_t), s->host_raw, n); /* fall back to the raw bytes */
+    if (!compression_enabled() || nccl_compress(raw, n, w + sizeof(uint64_t), &out) != 0 || out > wire - sizeof(uint64_t)) {
+        memcpy(w + sizeof(uint64_t), raw, n); /* fall back to the raw bytes */
         out = n;
     }
     uint64_t sz = out;
@@ -74,20 +94,24 @@ static int pack(stage_t *s, const void *buf, size_t n, cudaStream_t stream) {
     return cudaMemcpyAsync(s->dev_wire, w, wire, cudaMemcpyHostToDevice, stream) == cudaSuccess ? 0 : -1;
 }
 
-/* wire on the device (s->dev_wire) -> device data */
+/* wire on the device (s->dev_wire) -> caller's data (host directly, device through pinned memory) */
 static int unpack(stage_t *s, void *buf, size_t n, cudaStream_t stream) {
     const size_t wire = nccl_max_wire_size(n);
+    const int dev = on_device(buf);
+    if (dev && stage_reserve(s, n, wire)) return -1;
     if (cudaMemcpyAsync(s->host_wire, s->dev_wire, wire, cudaMemcpyDeviceToHost, stream) != cudaSuccess) return -1;
     if (cudaStreamSynchronize(stream) != cudaSuccess) return -1;
     unsigned char *w = (unsigned char *)s->host_wire;
     uint64_t sz = 0;
     memcpy(&sz, w, sizeof(sz));
     if (sz > wire - sizeof(uint64_t)) return -1;
-    if (!compression_enabled() || (sz == n && 0)) {
-        memcpy(s->host_raw, w + sizeof(uint64_t), n);
-    } else if (nccl_decompress(w + sizeof(uint64_t), (size_t)sz, s->host_raw, n) != 0) {
+    void *raw = dev ? s->host_raw : buf;
+    if (!compression_enabled()) {
+        memcpy(raw, w + sizeof(uint64_t), n);
+    } else if (nccl_decompress(w + sizeof(uint64_t), (size_t)sz, raw, n) != 0) {
         return -1;
     }
+    if (!dev) return 0;
     if (cudaMemcpyAsync(buf, s->host_raw, n, cudaMemcpyHostToDevice, stream) != cudaSuccess) return -1;
     return cudaStreamSynchronize(stream) == cudaSuccess ? 0 : -1;
 }
@@ -101,7 +125,7 @@ __attribute__((weak)) int nccl_send_compressed(const void *buf, size_t data_byte
 
 __attribute__((weak)) int nccl_recv_decompress(void *buf, size_t data_bytes, int peer, ncclComm_t comm, cudaStream_t stream) {
     if (data_bytes == 0) return 0;
-    if (stage_reserve(&g_recv, data_bytes, nccl_max_wire_size(data_bytes))) return 1;
+    if (stage_reserve(&g_recv, 0, nccl_max_wire_size(data_bytes))) return 1;
     if (ncclRecv(g_recv.dev_wire, nccl_max_wire_size(data_bytes), ncclUint8, peer, comm, stream) != ncclSuccess) return 1;
     return unpack(&g_recv, buf, data_bytes, stream) != 0;
 }
@@ -109,7 +133,7 @@ __attribute__((weak)) int nccl_recv_decompress(void *buf, size_t data_bytes, int
 __attribute__((weak)) int nccl_exchange_compressed(const void *sendbuf, size_t send_bytes, void *recvbuf, size_t recv_bytes, int dst,
                                                    int src, ncclComm_t comm, cudaStream_t stream) {
     if (send_bytes && pack(&g_send, sendbuf, send_bytes, stream)) return 1;
-    if (recv_bytes && stage_reserve(&g_recv, recv_bytes, nccl_max_wire_size(recv_bytes))) return 1;
+    if (recv_bytes && stage_reserve(&g_recv, 0, nccl_max_wire_size(recv_bytes))) return 1;
     if (ncclGroupStart() != ncclSuccess) return 1;
     int bad = 0;
     if (send_bytes) bad |= ncclSend(g_send.dev_wire, nccl_max_wire_size(send_bytes), ncclUint8, dst, comm, stream) != ncclSuccess;

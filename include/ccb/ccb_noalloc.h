@@ -29,8 +29,16 @@
  *    not cleared. Two calls that overlap on the GPU (different streams, or different
  *    host threads without ordering) race on it: issue calls on one stream, or order
  *    them yourself.
+ *  - A call returns CCB_OK once its kernel is launched. Every wait inside the kernel has
+ *    a time limit (10 s); a wait that runs out makes the kernel return early and leaves
+ *    `recv` partly written. That is NOT reported by the call that launched it: the
+ *    kernel records it in status words inside the array, and ccb_noalloc_status() reads
+ *    them back (a synchronising device-to-host copy of 32 bytes, no allocation). Call
+ *    it where a synchronisation is affordable, e.g. once per step after the stream has
+ *    been synchronised; a non-zero result means an earlier call's output must not be
+ *    used. The ordinary entry points report the same event through ccb_comm_status().
  *  - No cudaMalloc, cudaFree, or allocating library routine is called, here or in
- *    anything this entry point calls. */
+ *    anything these entry points call. */
 #ifndef CCB_NOALLOC_H
 #define CCB_NOALLOC_H
 
@@ -54,6 +62,12 @@ uint64_t ccb_noalloc_max_count(int nranks, int dtype, int codec);
  * `send` and `recv` are host arrays of nranks device pointers. Sum only. */
 int ccb_all_reduce_noalloc(const void* const* send, void* const* recv, int nranks, uint64_t count, int dtype, int codec,
                            ccb_stream_t stream);
+
+/* Status of the calls made so far on the current device: CCB_OK, or CCB_ERR_TIMEOUT
+ * when a device-side wait of an earlier call gave up (then `words`, if not null,
+ * receives the CCB_STATUS_WORDS status words: flags, where, epoch, last value seen).
+ * Synchronises with the device. */
+int ccb_noalloc_status(uint32_t* words);
 
 #ifdef __cplusplus
 }

@@ -4,7 +4,9 @@
  * Wire: [u64 compressed_size | payload | zero pad], always nccl_max_wire_size(n)
  * bytes so both sides post equal counts without a size hand-shake. Here
  * nccl_send_compressed / nccl_recv_decompress / nccl_exchange_compressed are weak
- * too, so a wrapper can replace the transport as well as the codec. */
+ * too, so a wrapper can replace the transport as well as the codec.
+ * `buf`, `sendbuf` and `recvbuf` are CPU (host) buffers, as in the reference; device or
+ * managed pointers are accepted as well and staged through pinned host memory. */
 #ifndef NCCL_COMPRESS_TOOLS_H
 #define NCCL_COMPRESS_TOOLS_H
 

@@ -52,6 +52,8 @@ def test_matches_the_ordinary_entry_point_twice(dtype, codec, n, count):
             scale = want[0].float().abs().max().item() + 1e-30
             step = {"int8": 1 / 127, "fp8": 1 / 8, "none": 2 ** -7 if dtype != torch.float32 else 1e-6}[codec]
             ulp = 0.0 if dtype == torch.float32 else 2.0 ** -7
+            words = (ctypes.c_uint32 * 8)()
+            assert lib().ccb_noalloc_status(words) == 0 and words[0] == 0, "no device-side wait may have given up"
             for r in range(n):
                 d = (got[r].float() - want[r].float()).abs().max().item()
                 assert d <= (2 * 1.01 * step + ulp) * scale, (call, r, d)
