@@ -13,8 +13,10 @@ NVSwitch peer memory). The reported value is nccl-tests bus bandwidth
 and the maximum over ranks; at N = 1 there is no bus, so the value is algbw of the
 local quantise/dequantise round trip the kernel still performs.
 
-`--impl reference` runs the reference's own allreduce benchmark binary under its own
-int8 wrapper (built unmodified from baseline/_ref) and prints the same line.
+`--impl reference` runs the reference's own allreduce benchmark binary (built unmodified
+under baseline/_ref) in its stock configuration, wrapper mode 0 = bare NCCL on the same
+bytes, and prints the same line; its int8 wrapper (mode 3) hung and then faulted on
+2 x B200 and is not run (baseline/reference_mode3_fault_record.txt).
 """
 from __future__ import annotations
 
@@ -38,7 +40,8 @@ def parse():
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "f32", "f16"])
     ap.add_argument("--codec", default="int8", choices=["int8", "fp8", "none", "int8_g256", "int4"])
     ap.add_argument("--algo", default="tune", choices=["tune", "auto", "twoshot", "oneshot", "ring", "tree", "nvls"],
-                    help="tune: time two-shot and ring on this message before the warm-up and keep the faster")
+                    help="tune: time two-shot and ring on this message before the warm-up; ring (one "
+                         "requantisation per hop) is kept only when it is more than 15 %% faster")
     ap.add_argument("--error-feedback", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -73,7 +76,7 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        comm = Communicator.from_torch_distributed(nvls=(args.algo == "nvls"))
+        comm = Communicator.from_torch_distributed(nvls=True)
     else:
         comm = Communicator.create(0, 1, f"bench{os.getpid()}")
 
@@ -89,8 +92,17 @@ def main():
         torch.cuda.synchronize()
 
     requested = args.algo
+    tuning = None
     if args.algo == "tune":
-        args.algo = comm.tune_all_reduce(x, y, codec=args.codec, algos=("twoshot", "ring")) if world > 1 else "twoshot"
+        if world > 1:
+            # the exact sum, for the error of each candidate
+            exact0 = x.float().clone()
+            dist.all_reduce(exact0)
+            args.algo, tuning = comm.tune_all_reduce(x, y, codec=args.codec, algos=("twoshot", "ring"), reference=exact0,
+                                                      prefer="twoshot", margin=0.15, report=True)
+            del exact0
+        else:
+            args.algo = "twoshot"
 
     def step():
         comm.all_reduce(x, y, codec=args.codec, algo=args.algo, error_feedback=ef)
@@ -152,8 +164,7 @@ def main():
     if not args.no_e2e:
         hx = torch.empty(count, dtype=dtype).pin_memory()
         hx.copy_(x)
-        sample = 16384
-        hy = torch.empty(sample, dtype=dtype).pin_memory()
+        hy = torch.empty(count, dtype=dtype).pin_memory()   # the whole result comes back every step
         copy_stream = torch.cuda.Stream()
         xin = [torch.empty_like(x), torch.empty_like(x)]
         ready = [torch.cuda.Event(), torch.cuda.Event()]
@@ -175,7 +186,7 @@ def main():
                 torch.cuda.current_stream().wait_event(ready[cur])
                 comm.all_reduce(xin[cur], y, codec=args.codec, algo=args.algo, error_feedback=ef)
                 freed[cur].record()
-                hy.copy_(y[:sample], non_blocking=True)
+                hy.copy_(y, non_blocking=True)
                 torch.cuda.current_stream().synchronize()
 
         e2e_loop(2)
@@ -195,18 +206,22 @@ def main():
         e2e = {"value": args.bytes / (e_ms * 1e-3) / 1e9 * factor * world, "unit": "GB/s",
                "busbw_per_gpu": args.bytes / (e_ms * 1e-3) / 1e9 * factor,
                "ms_per_step": e_ms, "wall_ms_per_step": wall_ms / args.steps,
-               "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": sample * hy.element_size()}
+               "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": count * hy.element_size(),
+               "note": "pinned host input uploaded and the full result read back every step; the upload of step "
+                       "i+1 overlaps the collective of step i"}
 
     factor = 2 * (world - 1) / world if world > 1 else 1.0
     algbw = args.bytes / (ms_per_step * 1e-3) / 1e9
     # roofline of the fused kernel: the wire bytes one GPU must push over NVLink at the
-    # 770 GB/s measured for a peer copy on this pool (one rank: input + output at the measured
-    # 6553 GB/s copy bandwidth)
+    # nominal 900 GB/s per direction (a peer copy measures 770 GB/s, SM-issued peer stores
+    # 711 GB/s); one rank: input + output at the measured 6553 GB/s copy bandwidth
     from ccbench_b200.comm import wire_bytes as _wire_bytes
 
     if world > 1:
-        bound_ms = factor * _wire_bytes(args.codec, dtype, count) / 770e9 * 1e3
-        roofline = {"bound": "nvlink", "gbs": 770, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step}
+        wire = factor * _wire_bytes(args.codec, dtype, count)
+        bound_ms = wire / 900e9 * 1e3
+        roofline = {"bound": "nvlink", "gbs": 900, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step,
+                    "fraction_of_measured_770": wire / 770e9 * 1e3 / ms_per_step}
     else:
         bound_ms = 2 * args.bytes / 6553e9 * 1e3
         roofline = {"bound": "hbm", "gbs": 6553, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step}
@@ -223,7 +238,9 @@ def main():
             "config": {"model": "gradient-like buffer: Laplace(0,1e-3) + 0.1% x100 outliers",
                        "global_batch": args.bytes * world, "seq_len": count,
                        "message_bytes_per_rank": args.bytes, "codec": args.codec, "algo": args.algo,
-                       "algo_selection": "measured before warm-up: two-shot vs ring" if requested == "tune" else "fixed",
+                       "algo_selection": ("measured before warm-up; ring (n requantisations) only if > 15 % faster than "
+                                          "two-shot (2 requantisations)") if requested == "tune" else "fixed",
+                       "algo_candidates": tuning,
                        "error_feedback": bool(args.error_feedback),
                        "parallelism": f"dp{world}", "l2": "inputs (256 MiB) larger than L2, no flush needed",
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},

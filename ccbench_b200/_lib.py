@@ -18,11 +18,11 @@ LIBCCB = NATIVE_DIR / "libccb.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC", "-shared", "--threads", "0",
 ]
 
 RT_SOURCES = ["csrc/rt/ccb_rt.cu", "csrc/rt/ccb_bootstrap.cpp", "csrc/kernels/ccb_standalone.cu",
-              "csrc/kernels/ccb_sz.cu", "csrc/kernels/ccb_moe.cu", "csrc/kernels/ccb_noalloc.cu"]
+              "csrc/kernels/ccb_sz.cu", "csrc/kernels/ccb_moe.cu", "csrc/kernels/ccb_noalloc.cu", "csrc/kernels/ccb_pipe.cu"]
 
 
 def _nvcc() -> str:

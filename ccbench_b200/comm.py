@@ -111,7 +111,7 @@ class Communicator:
 
     def set_pipeline(self, mode: int = 1, link_warps: int = 0, multicast: bool = True) -> None:
         """The warp-specialised pipelined two-shot kernel: mode 0 never, 1 when the message is
-        large enough, 2 always; link_warps of a CTA's 15 data warps store over NVLink (0 keeps
+        large enough, 2 always; link_warps of a CTA's 31 data warps store over NVLink (0 keeps
         the current value); multicast lets phase 2 store once through an NVLS mapping."""
         L = lib()
         L.ccb_comm_set_pipeline.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
@@ -177,17 +177,25 @@ class Communicator:
         return recv
 
     def tune_all_reduce(self, send: Tensors, recv: Tensors, *, codec="int8", algos=("twoshot", "ring", "oneshot"),
-                        iters: int = 3) -> str:
+                        iters: int = 3, reference: Optional[torch.Tensor] = None, prefer: Optional[str] = None,
+                        margin: float = 0.15, report: bool = False):
         """Times each algorithm on these very buffers (CUDA events, maximum over the ranks
-        of an initialised torch.distributed group), remembers the fastest for this
+        of an initialised torch.distributed group), remembers the choice for this
         (element count, dtype, codec) and returns its name; all_reduce(algo="auto") then
         uses it. Every rank must call it with the same arguments. Candidates that do not
-        fit the arena (one-shot on large messages) are skipped."""
+        fit the arena (one-shot on large messages) are skipped.
+
+        The choice is the fastest candidate, under an error cap: when `prefer` names a
+        candidate (the shape with the fewest requantisations, "twoshot"), another one
+        replaces it only if it is more than `margin` faster. With `reference` (the exact
+        fp32 result) each candidate's relative L2 error is measured too; `report=True`
+        returns (name, {algo: {"ms": ..., "rel_l2": ...}})."""
         import torch.distributed as dist
 
         _, st = self._ptrs(send, "send")
+        _, rt = self._ptrs(recv, "recv")
         dist_up = dist.is_available() and dist.is_initialized() and self.nlocal == 1 and self.nranks > 1
-        best, best_t = "auto", float("inf")
+        seen = {}
         for algo in algos:
             wire = wire_bytes(codec, st[0].dtype, st[0].numel())
             if algo == "oneshot" and wire * self.nranks > self.arena_bytes // 2 - (1 << 20):
@@ -203,15 +211,19 @@ class Communicator:
                 self.all_reduce(send, recv, codec=codec, algo=algo)
             e1.record()
             torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=st[0].device)
+            t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=st[0].device)
             if dist_up:
                 dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            if t.item() < best_t:
-                best, best_t = algo, t.item()
+            seen[algo] = {"ms": t.item()}
+            if reference is not None:
+                seen[algo]["rel_l2"] = ((rt[0].float() - reference).norm() / reference.norm()).item()
+        best = min(seen, key=lambda a: seen[a]["ms"]) if seen else "auto"
+        if prefer in seen and best != prefer and seen[best]["ms"] > (1.0 - margin) * seen[prefer]["ms"]:
+            best = prefer
         if not hasattr(self, "_tuned"):
             self._tuned = {}
         self._tuned[(st[0].numel(), st[0].dtype, codec)] = best
-        return best
+        return (best, seen) if report else best
 
     def reduce_scatter(self, send: Tensors, recv: Tensors, *, op="sum", codec="int8",
                        error_feedback: Optional[Tensors] = None):

@@ -104,13 +104,15 @@ struct CodecInt8 {
     for (int d = 1; d < kLanes; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
     const float inv = m > 0.f ? 127.f / m : 0.f;
     pk.scale = m / 127.f;
+    // Round to nearest even without a float-to-int conversion: adding 1.5 * 2^23 leaves the
+    // integer (|v * inv| <= 127) in the low mantissa bits, two's complement in the low byte;
+    // the product is rounded to fp32 first (no fused multiply-add), so the code is the
+    // same as round-half-even of the fp32 product, which is what the restatements compute.
+    auto q8 = [&](float x) { return __float_as_uint(__fadd_rn(__fmul_rn(x, inv), 12582912.f)); };
     uint32_t w[4];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      int a = __float2int_rn(v[4 * k] * inv), b = __float2int_rn(v[4 * k + 1] * inv);
-      int c = __float2int_rn(v[4 * k + 2] * inv), d = __float2int_rn(v[4 * k + 3] * inv);
-      w[k] = (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
-    }
+    for (int k = 0; k < 4; ++k)
+      w[k] = __byte_perm(__byte_perm(q8(v[4 * k]), q8(v[4 * k + 1]), 0x0040), __byte_perm(q8(v[4 * k + 2]), q8(v[4 * k + 3]), 0x0040), 0x5410);
     pk.q = make_uint4(w[0], w[1], w[2], w[3]);
   }
   static __device__ __forceinline__ void decode(const Packet& pk, float (&v)[16]) {

@@ -207,6 +207,74 @@ __device__ __forceinline__ void load16(const T* base, size_t idx, size_t limit, 
   }
 }
 
+// The same load split in two, so that a thread can issue the loads of several lanes
+// before it converts the first: the 16 elements as raw 16-byte vectors. Everything is
+// written with register moves and bit operations (no pointer into the vectors), so the
+// raw values stay in registers.
+template <class T> struct Raw16 { uint4 q[sizeof(T)]; };
+__device__ __forceinline__ uint32_t elem_bits(float x) { return __float_as_uint(x); }
+__device__ __forceinline__ uint32_t elem_bits(__nv_bfloat16 x) { return __bfloat16_as_ushort(x); }
+__device__ __forceinline__ uint32_t elem_bits(__half x) { return __half_as_ushort(x); }
+template <class T> __device__ __forceinline__ float bits_to_f(uint32_t b);
+template <> __device__ __forceinline__ float bits_to_f<float>(uint32_t b) { return __uint_as_float(b); }
+template <> __device__ __forceinline__ float bits_to_f<__nv_bfloat16>(uint32_t b) { return __uint_as_float(b << 16); }
+template <> __device__ __forceinline__ float bits_to_f<__half>(uint32_t b) { return __half2float(__ushort_as_half((unsigned short)b)); }
+
+template <class T>
+__device__ __forceinline__ void load16_raw(const T* base, size_t idx, size_t limit, Raw16<T>& raw) {
+  const T* p = base + idx;
+  if (idx + 16 <= limit && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+#pragma unroll
+    for (int k = 0; k < (int)sizeof(T); ++k) raw.q[k] = ldg_stream(reinterpret_cast<const char*>(p) + 16 * k);
+  } else {
+    uint32_t w[4 * sizeof(T)];
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) w[i] = (idx + i < limit) ? elem_bits(p[i]) : 0u;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t lo = (idx + 2 * i < limit) ? elem_bits(p[2 * i]) : 0u;
+        const uint32_t hi = (idx + 2 * i + 1 < limit) ? elem_bits(p[2 * i + 1]) : 0u;
+        w[i] = lo | (hi << 16);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < (int)sizeof(T); ++k) raw.q[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+  }
+}
+template <class T>
+__device__ __forceinline__ void raw16_to_f(const Raw16<T>& raw, float (&v)[16]) {
+#pragma unroll
+  for (int k = 0; k < (int)sizeof(T); ++k) {
+    const uint32_t w[4] = {raw.q[k].x, raw.q[k].y, raw.q[k].z, raw.q[k].w};
+    if constexpr (sizeof(T) == 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) v[4 * k + i] = bits_to_f<T>(w[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[8 * k + 2 * i] = bits_to_f<T>(w[i] & 0xffffu);
+        v[8 * k + 2 * i + 1] = bits_to_f<T>(w[i] >> 16);
+      }
+    }
+  }
+}
+
+// Two fp32 values rounded to nearest even and packed into one 32-bit word (lo in the low half).
+template <class T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <> __device__ __forceinline__ uint32_t pack2<float>(float lo, float) { return __float_as_uint(lo); }
+
 template <class T>
 __device__ __forceinline__ void store16(T* base, size_t idx, size_t limit, const float (&v)[16]) {
   T* p = base + idx;
@@ -221,10 +289,9 @@ __device__ __forceinline__ void store16(T* base, size_t idx, size_t limit, const
     } else {
 #pragma unroll
       for (int k = 0; k < 2; ++k) {
-        uint4 u;
-        T* h = reinterpret_cast<T*>(&u);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) h[i] = Elem<T>::from_f(v[8 * k + i]);
+        // one packed conversion per pair of values
+        const uint4 u = make_uint4(pack2<T>(v[8 * k], v[8 * k + 1]), pack2<T>(v[8 * k + 2], v[8 * k + 3]),
+                                   pack2<T>(v[8 * k + 4], v[8 * k + 5]), pack2<T>(v[8 * k + 6], v[8 * k + 7]));
         stg_stream(reinterpret_cast<char*>(p) + 16 * k, u);
       }
     }

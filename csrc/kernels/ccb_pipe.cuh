@@ -8,7 +8,7 @@
 //                          ONE multimem.st per lane where the arenas have an NVLS mapping)
 //   decode warps  P3(w)  : decode the reduced shards into recv               (HBM only)
 //                 (ReduceScatter: they run the reduction P2 instead; there is no P3)
-//   signal warp   owns every fence.acq_rel.sys + flag store: the link warps hand a phase
+//   signal warp   (the last of the CTA's 32) owns every fence.acq_rel.sys + flag store: the link warps hand a phase
 //                 over through a shared-memory counter and go on storing, so the
 //                 20 us a system fence costs under store load is off their path.
 //
@@ -29,8 +29,10 @@ constexpr int kPipeChunkShift = 3;                    // a CTA owns runs of 8 un
 constexpr int kPipeChunkUnits = 1 << kPipeChunkShift;
 
 struct PipeShared {
-  unsigned int p1_done;    // link-warp arrivals after phase 1, summed over the waves
-  unsigned int p2_done;    // the same after phase 2
+  // Warp arrivals after phase 1 / phase 2 of each wave. One counter per wave: warps drift
+  // apart by more than a wave, so a running total would mix arrivals of different waves.
+  unsigned int p1_done[CCB_MAX_SLOTS / 2];
+  unsigned int p2_done[CCB_MAX_SLOTS / 2];
   unsigned int p1_ready;   // waves whose phase-1 flags from all peers have been seen
   unsigned int p2_ready;   // the same for phase 2
   int fail;
@@ -149,14 +151,21 @@ __device__ __forceinline__ void warp_arrive(unsigned int* ctr) {
   if ((threadIdx.x & 31) == 0) red_release_cta_shared_add(ctr, 1u);
 }
 
+// 1024 threads: 32 warps per SM at 64 registers. The phases are bound by instruction issue
+// as much as by memory (about 25 instructions per element over the three phases), so the
+// kernel needs the occupancy; the loops below therefore keep one item per warp in flight
+// and leave latency hiding to the 32 resident warps.
+constexpr int kPipeThreads = 1024;
+constexpr int kPipeWarps = kPipeThreads / 32;
+
 template <class T, class C>
-__global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant__ ReduceArgs a) {
+__global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_constant__ ReduceArgs a) {
   __shared__ PipeShared sh;
   const CommDev& c = a.c;
   const int lr = blockIdx.y, r = a.rank0 + lr, n = c.nranks;
   const size_t b = blockIdx.x, G = gridDim.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int L = a.link_warps, D = kWarps - 1 - L;  // warp kWarps-1 signals
+  const int L = a.link_warps, D = kPipeWarps - 1 - L;  // the last warp signals
   const int W = a.waves;
   const bool ar = (a.mode == CCB_MODE_ALLREDUCE);
   const T* send = static_cast<const T*>(a.send[lr]);
@@ -169,7 +178,8 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
   const bool use_mc = a.use_mc && c.mc_arena != nullptr;
   const uint32_t peers = ((1u << n) - 1u) & ~(1u << r);
   if (threadIdx.x == 0) {
-    sh.p1_done = sh.p2_done = sh.p1_ready = sh.p2_ready = 0u;
+    for (int w = 0; w < CCB_MAX_SLOTS / 2; ++w) sh.p1_done[w] = sh.p2_done[w] = 0u;
+    sh.p1_ready = sh.p2_ready = 0u;
     sh.fail = 0;
   }
   __syncthreads();  // the only CTA-wide barrier: the roles part ways here
@@ -194,6 +204,17 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
     return ((ch << kPipeChunkShift) + (i & (kPipeChunkUnits - 1))) * kWarpElems;
   };
 
+  const bool sum = (a.op == CCB_OP_SUM);
+  auto accumulate = [&](float (&acc)[16], const float (&d)[16]) {
+    if (sum) {
+#pragma unroll
+      for (int k = 0; k < 16; ++k) acc[k] += d[k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < 16; ++k) acc[k] = apply_op(a.op, acc[k], d[k]);
+    }
+  };
+
   // ---- phase 1 of wave w: this rank's lanes of every peer's shard, to the owner ----
   auto phase1 = [&](int w, int gw, int gn) {
     for (int j = 1; j < n; ++j) {
@@ -204,34 +225,28 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
       char* dst = c.arena[p] + area1 + (size_t)r * a.slot_bytes;
       size_t kb;
       const size_t items = wave_items(valid, w, kb);
-      for (size_t i = gw; i < items; i += 2 * (size_t)gn) {
+      for (size_t i = gw; i < items; i += gn) {
         const size_t e0 = item_elem(kb, i);
-        const size_t i1 = i + gn;
-        const size_t e1 = i1 < items ? item_elem(kb, i1) : valid;
-        float v0[16], v1[16];
-        const bool h0 = e0 < valid, h1 = e1 < valid;
-        if (h0) load16<T>(src, e0 + lane * kLaneElems, valid, v0);
-        if (h1) load16<T>(src, e1 + lane * kLaneElems, valid, v1);
-        auto one = [&](size_t idx, float (&v)[16]) {
-          if (efs) {
-            float e[16];
-            load16f_plain(efs, idx, valid, e);
+        if (e0 >= valid) continue;
+        const size_t idx = e0 + lane * kLaneElems;
+        float v[16];
+        load16<T>(src, idx, valid, v);
+        if (efs) {
+          float e[16];
+          load16f_plain(efs, idx, valid, e);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) v[q] += e[q];
-          }
-          typename C::Packet pk;
-          C::encode(v, pk);
-          C::store(dst, pad, idx, pk);
-          if (efs) {
-            float d[16];
-            C::decode(pk, d);
+          for (int q = 0; q < 16; ++q) v[q] += e[q];
+        }
+        typename C::Packet pk;
+        C::encode(v, pk);
+        C::store(dst, pad, idx, pk);
+        if (efs) {
+          float d[16];
+          C::decode(pk, d);
 #pragma unroll
-            for (int q = 0; q < 16; ++q) d[q] = v[q] - d[q];
-            store16f_plain(efs, idx, valid, d);
-          }
-        };
-        if (h0) one(e0 + lane * kLaneElems, v0);
-        if (h1) one(e1 + lane * kLaneElems, v1);
+          for (int q = 0; q < 16; ++q) d[q] = v[q] - d[q];
+          store16f_plain(efs, idx, valid, d);
+        }
       }
     }
   };
@@ -250,23 +265,13 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
       const size_t idx = e0 + lane * kLaneElems;
       float acc[16];
       load16<T>(src, idx, valid, acc);
-      // The sources' packets are fetched in batches before any is decoded, so that a lane
-      // has several loads in flight instead of one round trip to memory per source.
-      constexpr int kBatch = sizeof(typename C::Packet) <= 32 ? 4 : 2;
-      for (int q0 = 0; q0 < n; q0 += kBatch) {
-        typename C::Packet in[kBatch];
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k)
-          if (q0 + k < n && q0 + k != r) C::load(my + area1 + (size_t)(q0 + k) * a.slot_bytes, pad, idx, in[k]);
-#pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-          if (q0 + k < n && q0 + k != r) {
-            float d[16];
-            C::decode(in[k], d);
-#pragma unroll
-            for (int e = 0; e < 16; ++e) acc[e] = apply_op(a.op, acc[e], d[e]);
-          }
-        }
+      for (int q = 0; q < n; ++q) {  // increasing rank order, as in reduce_kernel
+        if (q == r) continue;
+        typename C::Packet pk;
+        C::load(my + area1 + (size_t)q * a.slot_bytes, pad, idx, pk);
+        float d[16];
+        C::decode(pk, d);
+        accumulate(acc, d);
       }
       if (!ar) {  // ReduceScatter delivers the fp32 sum without a second quantisation
         store16<T>(out, idx, valid, acc);
@@ -306,23 +311,14 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
       T* out = recv + (size_t)q * a.shard_elems;
       size_t kb;
       const size_t items = wave_items(valid, w, kb);
-      for (size_t i = gw; i < items; i += 2 * (size_t)gn) {
+      for (size_t i = gw; i < items; i += gn) {
         const size_t e0 = item_elem(kb, i);
-        const size_t i1 = i + gn;
-        const size_t e1 = i1 < items ? item_elem(kb, i1) : valid;
-        const bool h0 = e0 < valid, h1 = e1 < valid;
-        typename C::Packet p0, p1;
-        if (h0) C::load(slot, pad, e0 + lane * kLaneElems, p0);
-        if (h1) C::load(slot, pad, e1 + lane * kLaneElems, p1);
+        if (e0 >= valid) continue;
+        typename C::Packet pk;
+        C::load(slot, pad, e0 + lane * kLaneElems, pk);
         float d[16];
-        if (h0) {
-          C::decode(p0, d);
-          store16<T>(out, e0 + lane * kLaneElems, valid, d);
-        }
-        if (h1) {
-          C::decode(p1, d);
-          store16<T>(out, e1 + lane * kLaneElems, valid, d);
-        }
+        C::decode(pk, d);
+        store16<T>(out, e0 + lane * kLaneElems, valid, d);
       }
     }
   };
@@ -332,29 +328,40 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
     if (tr) c.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * CCB_TRACE_SLOTS + k] = globaltimer_ns();
   };
 
+  // Ramp-up and ramp-down: before the first phase-2 flags can arrive the decode warps have
+  // nothing to do, and after the last phase 2 the link warps have nothing left, so in an
+  // AllReduce all 31 data warps share phase 1 of wave 0 and phase 3 of the last wave.
+  const int kData = kPipeWarps - 1;
   if (warp < L) {
     // ------------------------------------------------------------ link warps ----
     const bool leader = (warp == 0);
+    uint64_t waited = 0;  // trace slot 6: ns the link leader spent waiting for phase-1 flags
     if (leader) mark(0);
-    phase1(0, warp, L);
-    warp_arrive(&sh.p1_done);
+    if (ar) phase1(0, warp, kData); else phase1(0, warp, L);
+    warp_arrive(&sh.p1_done[0]);
     if (leader) mark(1);
     if (ar) {
       for (int w = 0; w < W; ++w) {
         if (w + 1 < W) {
           phase1(w + 1, warp, L);
-          warp_arrive(&sh.p1_done);
+          warp_arrive(&sh.p1_done[w + 1]);
         }
+        const uint64_t tw0 = tr ? globaltimer_ns() : 0;
         if (!group_wait(leader, &sh.p1_ready, w, 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
+        if (tr) waited += globaltimer_ns() - tw0;
         phase2(w, warp, L);
-        warp_arrive(&sh.p2_done);
+        warp_arrive(&sh.p2_done[w]);
         if (leader && w == 0) mark(2);
       }
       if (leader) mark(3);
+      if (leader && tr) c.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * CCB_TRACE_SLOTS + 6] = waited;
+      // the last wave's decode, shared with the decode warps (whose leader polls the flags)
+      if (!warp_wait_counter(&sh.p2_ready, (unsigned)W, sh, c, my, 0x20 | ((W - 1) << 16) | 0x8000)) return;
+      phase3(W - 1, warp, kData);
     } else {
       for (int w = 1; w < W; ++w) {
         phase1(w, warp, L);
-        warp_arrive(&sh.p1_done);
+        warp_arrive(&sh.p1_done[w]);
       }
       if (leader) mark(3);
     }
@@ -362,10 +369,14 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
     // ---------------------------------------------------------- decode warps ----
     const int gw = warp - L;
     const bool leader = (gw == 0);
+    if (ar) {
+      phase1(0, warp, kData);
+      warp_arrive(&sh.p1_done[0]);
+    }
     for (int w = 0; w < W; ++w) {
       if (ar) {
         if (!group_wait(leader, &sh.p2_ready, w, 2 * w + 1, c, my, r, sh, 0x20 | (w << 16))) return;
-        phase3(w, gw, D);
+        if (w + 1 < W) phase3(w, gw, D); else phase3(w, warp, kData);
       } else {
         if (!group_wait(leader, &sh.p1_ready, w, 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
         phase2(w, gw, D);
@@ -376,22 +387,28 @@ __global__ void __launch_bounds__(kThreads, 1) pipe_kernel(const __grid_constant
   } else {
     // ----------------------------------------------------------- signal warp ----
     // Events in the order the link warps produce them: P1(0), then per wave P1(w+1), P2(w).
+    // Phase 1 of wave 0 has kData arrivals in an AllReduce (everybody helps), L otherwise.
+    const unsigned first = ar ? (unsigned)kData : (unsigned)L;
+    uint64_t fenced = 0;  // trace slot 7: ns spent in fences and flag stores
     auto publish = [&](int row) {
+      const uint64_t t0 = tr ? globaltimer_ns() : 0;
       if (lane == 0) signal_peers(c, peers, row, r, (int)b);
       __syncwarp();
+      if (tr) fenced += globaltimer_ns() - t0;
     };
-    if (!warp_wait_counter(&sh.p1_done, (unsigned)L, sh, c, my, 0xA0)) return;
+    if (!warp_wait_counter(&sh.p1_done[0], first, sh, c, my, 0xA0)) return;
     publish(0);
     for (int w = 0; w < W; ++w) {
       if (w + 1 < W) {
-        if (!warp_wait_counter(&sh.p1_done, (unsigned)(L * (w + 2)), sh, c, my, 0xA0 | ((w + 1) << 16))) return;
+        if (!warp_wait_counter(&sh.p1_done[w + 1], (unsigned)L, sh, c, my, 0xA0 | ((w + 1) << 16))) return;
         publish(2 * (w + 1));
       }
       if (ar) {
-        if (!warp_wait_counter(&sh.p2_done, (unsigned)(L * (w + 1)), sh, c, my, 0xB0 | (w << 16))) return;
+        if (!warp_wait_counter(&sh.p2_done[w], (unsigned)L, sh, c, my, 0xB0 | (w << 16))) return;
         publish(2 * w + 1);
       }
     }
+    if (tr) c.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * CCB_TRACE_SLOTS + 7] = fenced;
   }
 }
 

@@ -20,7 +20,6 @@
 
 #include "../kernels/ccb_exchange.cuh"
 #include "../kernels/ccb_nvls.cuh"
-#include "../kernels/ccb_pipe.cuh"
 #include "../kernels/ccb_reduce.cuh"
 #include "../kernels/ccb_ring.cuh"
 #include "ccb/ccb.h"
@@ -146,7 +145,7 @@ struct ccb_comm {
   int waves = 0;  // 0 = choose per call
   int pipe_mode = 1;        // 0 = never use the pipelined two-shot kernel, 1 = when large enough, 2 = always
   int pipe_min_chunks = 4;  // chunks (4096 elements) per CTA from which it is used
-  int pipe_link_warps = 10; // of the 15 data warps, how many store over NVLink
+  int pipe_link_warps = 24; // of the 31 data warps of a CTA, how many store over NVLink
   int pipe_mc = 1;          // phase 2 through the NVLS multicast mapping when there is one
   unsigned long long* trace = nullptr;  // device buffer, CCB_MAX_CTAS * nlocal * CCB_TRACE_SLOTS
   bool dead = false;
@@ -180,9 +179,9 @@ static int finish_common(ccb_comm* c) {
   c->waves = (int)env_u64("CCB_WAVES", 0);
   c->pipe_mode = (int)env_u64("CCB_PIPE", 1);
   c->pipe_min_chunks = (int)env_u64("CCB_PIPE_MIN_CHUNKS", 4);
-  c->pipe_link_warps = (int)env_u64("CCB_PIPE_LINK_WARPS", 10);
+  c->pipe_link_warps = (int)env_u64("CCB_PIPE_LINK_WARPS", 24);
   if (c->pipe_link_warps < 1) c->pipe_link_warps = 1;
-  if (c->pipe_link_warps > kWarps - 2) c->pipe_link_warps = kWarps - 2;
+  if (c->pipe_link_warps > 30) c->pipe_link_warps = 30;
   c->pipe_mc = (int)env_u64("CCB_PIPE_MC", 1);
   RT_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), CCB_STATUS_WORDS * 4, cudaHostAllocMapped));
   memset(c->status_host, 0, CCB_STATUS_WORDS * 4);
@@ -213,9 +212,9 @@ uint32_t next_epoch(ccb_comm* c) {
 
 // How many CTAs per rank may be launched so that every CTA of every local rank is
 // resident at once (CTAs spin on flags written by same-numbered CTAs elsewhere).
-int grid_cap(ccb_comm* c, const void* kernel) {
+int grid_cap(ccb_comm* c, const void* kernel, int threads) {
   int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, 0) != cudaSuccess || per_sm < 1) {
     (void)cudaGetLastError();
     per_sm = 1;
   }
@@ -226,8 +225,8 @@ int grid_cap(ccb_comm* c, const void* kernel) {
   return cap < 1 ? 1 : cap;
 }
 
-int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream) {
-  dim3 grid((unsigned)ctas, (unsigned)c->nlocal, 1), block(kThreads, 1, 1);
+int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream, int threads) {
+  dim3 grid((unsigned)ctas, (unsigned)c->nlocal, 1), block((unsigned)threads, 1, 1);
   void* params[] = {args};
   cudaError_t e = cudaLaunchCooperativeKernel(kernel, grid, block, params, 0, stream);
   if (e != cudaSuccess) {
@@ -590,9 +589,9 @@ extern "C" int ccb_comm_set_waves(ccb_comm* c, int waves) {
   return CCB_OK;
 }
 /* Pipelined two-shot kernel: mode 0 never / 1 when the message is large enough / 2 always;
- * link_warps in [1, 14] (0 keeps the current value); mc != 0 lets phase 2 use the NVLS mapping. */
+ * link_warps in [1, 30] (0 keeps the current value); mc != 0 lets phase 2 use the NVLS mapping. */
 extern "C" int ccb_comm_set_pipeline(ccb_comm* c, int mode, int link_warps, int mc) {
-  if (!c || mode < 0 || mode > 2 || link_warps < 0 || link_warps > kWarps - 2) return CCB_ERR_ARG;
+  if (!c || mode < 0 || mode > 2 || link_warps < 0 || link_warps > 30) return CCB_ERR_ARG;
   c->pipe_mode = mode;
   if (link_warps > 0) c->pipe_link_warps = link_warps;
   c->pipe_mc = mc ? 1 : 0;
@@ -640,9 +639,6 @@ static const void* reduce_fn(int dtype, int codec, int shape) {
   if (shape == kOneShot) return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&reduce_kernel<TT, CC, kOneShot>)));
   return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&reduce_kernel<TT, CC, kTwoShot>)));
 }
-static const void* pipe_fn(int dtype, int codec) {
-  return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&pipe_kernel<TT, CC>)));
-}
 static const void* exchange_fn(int dtype, int codec) {
   return CCB_DISPATCH_TC(dtype, codec, (reinterpret_cast<const void*>(&exchange_kernel<TT, CC>)));
 }
@@ -681,13 +677,13 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
   // kernel: it needs a few chunks (8 units of 512 elements) per CTA and wave to pay.
   int pipe_waves = 0, pipe_ctas = 0;
   if (shape == kTwoShot && mode != CCB_MODE_REDUCE && c->nranks > 1 && c->pipe_mode != 0) {
-    const void* pfn = pipe_fn(dtype, codec);
-    const int cap = grid_cap(c, pfn);
+    const void* pfn = pipe_kernel_fn(dtype, codec);
+    const int cap = pfn ? grid_cap(c, pfn, pipe_kernel_threads()) : 1;
     const size_t per = shard_elems < count ? shard_elems : count;
-    const size_t chunks = (per + (size_t)kWarpElems * kPipeChunkUnits - 1) / ((size_t)kWarpElems * kPipeChunkUnits);
+    const size_t chunks = (per + kPipeChunkElems - 1) / kPipeChunkElems;
     const size_t ctas = chunks < (size_t)cap ? chunks : (size_t)cap;
     const size_t per_cta = ctas ? chunks / ctas : 0;
-    if (per_cta >= (size_t)c->pipe_min_chunks || c->pipe_mode == 2) {
+    if (pfn && (per_cta >= (size_t)c->pipe_min_chunks || c->pipe_mode == 2)) {
       int w = c->waves > 0 ? c->waves : (int)(per_cta / 2);
       if (w > CCB_MAX_SLOTS / 2) w = CCB_MAX_SLOTS / 2;
       if (w < 1) w = 1;
@@ -719,7 +715,7 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
     a.tile_warps = kWarps;
     a.link_warps = c->pipe_link_warps;
     a.use_mc = (c->mc_arena && c->nlocal == 1 && c->pipe_mc) ? 1 : 0;
-    return launch(c, fn, pipe_ctas, &a, stream);
+    return launch(c, fn, pipe_ctas, &a, stream, pipe_kernel_threads());
   }
   const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count, &a.tile_warps);
   // Each extra wave of the non-specialised kernel costs a pipeline drain (fence + flag

@@ -54,8 +54,8 @@ int ccb_comm_set_max_ctas(ccb_comm* c, int ctas);
 int ccb_comm_set_waves(ccb_comm* c, int waves);
 /* The warp-specialised pipelined two-shot kernel (large AllReduce / ReduceScatter):
  * mode 0 = never, 1 = when the message is large enough (default), 2 = always;
- * link_warps = how many of a CTA's 15 data warps store over NVLink (0 keeps the current
- * value, default 10; the rest decode); mc != 0 lets its second phase store once to the
+ * link_warps = how many of a CTA's 31 data warps store over NVLink (1 to 30; 0 keeps the
+ * current value, default 24; the rest decode); mc != 0 lets its second phase store once to the
  * NVLS multicast address when the communicator has one. Also CCB_PIPE,
  * CCB_PIPE_LINK_WARPS, CCB_PIPE_MC, CCB_PIPE_MIN_CHUNKS in the environment. */
 int ccb_comm_set_pipeline(ccb_comm* c, int mode, int link_warps, int mc);

@@ -91,7 +91,7 @@ def test_all_reduce_matches_plain_kernel(comms, codec, dt, n, count, waves):
         assert frac < 0.02, f"{frac:.4f} of elements differ from the restated algorithm"
 
 
-@pytest.mark.parametrize("link_warps", [1, 7, 14])
+@pytest.mark.parametrize("link_warps", [1, 15, 30])
 def test_role_splits(comms, link_warps):
     n, count = 4, 600_000
     comm = comms(n)
@@ -108,7 +108,7 @@ def test_role_splits(comms, link_warps):
     comm.set_waves(3)
     comm.set_pipeline(2, link_warps=link_warps)
     piped = run()
-    comm.set_pipeline(1, link_warps=10)
+    comm.set_pipeline(1, link_warps=24)
     comm.set_waves(0)
     assert comm.status()[0] == 0
     for r in range(n):
@@ -116,7 +116,7 @@ def test_role_splits(comms, link_warps):
 
 
 @pytest.mark.parametrize("codec", ["int8", "fp8", "none"])
-@pytest.mark.parametrize("n,per,waves", [(2, 512, 1), (4, 10007, 2), (8, 400_000, 4)])
+@pytest.mark.parametrize("n,per,waves", [(2, 512, 1), (4, 10007, 2), (8, 400_000, 4), (8, 700_001, 8)])
 def test_reduce_scatter_matches_plain_kernel(comms, codec, n, per, waves):
     comm = comms(n)
     comm.set_waves(waves)
