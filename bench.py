@@ -44,6 +44,9 @@ def parse():
                          "requantisation per hop) is kept only when it is more than 15 %% faster")
     ap.add_argument("--error-feedback", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--via", default="api", choices=["api", "interposer"],
+                    help="interposer: also run the same collective through the NCCL benchmark driver under "
+                         "LD_PRELOAD=libccb_nccl.so and report its device time beside the direct-API time")
     return ap.parse_args()
 
 
@@ -210,6 +213,17 @@ def main():
                "note": "pinned host input uploaded and the full result read back every step; the upload of step "
                        "i+1 overlaps the collective of step i"}
 
+    # ---- the same collective through the LD_PRELOAD interposer and the C benchmark driver ----
+    interposed = None
+    if args.via == "interposer" and world > 1:
+        from ccbench_b200.bench import via_interposer
+
+        interposed = via_interposer.run(x, rank=rank, world=world, local_rank=local_rank, nbytes=args.bytes, dtype=args.dtype,
+                                        codec=args.codec, algo=args.algo, steps=args.steps, warmup=args.warmup)
+        if rank == 0 and interposed and "ms_per_step" in interposed:
+            interposed["direct_api_ms_per_step"] = ms_per_step
+            interposed["interposed_over_direct"] = interposed["ms_per_step"] / ms_per_step
+
     factor = 2 * (world - 1) / world if world > 1 else 1.0
     algbw = args.bytes / (ms_per_step * 1e-3) / 1e9
     # roofline of the fused kernel: the wire bytes one GPU must push over NVLink at the
@@ -246,7 +260,7 @@ def main():
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},
             "algbw": algbw, "ref_definition_bw": 2 * algbw, "compression_ratio": wire_ratio(args.codec, dtype),
             "rel_l2_error": rel_l2, "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "e2e": e2e, "gpu_launches": launches, "host_numa_binding": numa, "roofline": roofline,
+            "e2e": e2e, "via_interposer": interposed, "gpu_launches": launches, "host_numa_binding": numa, "roofline": roofline,
         }
         print(json.dumps(line), flush=True)
     comm.close()

@@ -22,7 +22,8 @@ NVCC_FLAGS = [
 ]
 
 RT_SOURCES = ["csrc/rt/ccb_rt.cu", "csrc/rt/ccb_bootstrap.cpp", "csrc/kernels/ccb_standalone.cu",
-              "csrc/kernels/ccb_sz.cu", "csrc/kernels/ccb_moe.cu", "csrc/kernels/ccb_noalloc.cu", "csrc/kernels/ccb_pipe.cu"]
+              "csrc/kernels/ccb_sz.cu", "csrc/kernels/ccb_moe.cu", "csrc/kernels/ccb_noalloc.cu", "csrc/kernels/ccb_pipe.cu",
+              "csrc/kernels/ccb_lossless.cu"]
 
 
 def _nvcc() -> str:

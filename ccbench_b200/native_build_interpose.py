@@ -20,6 +20,9 @@ def build(verbose: bool = False) -> None:
     for name, src, extra in [
         ("libnccl_compress_tools.so", root / "csrc/wrappers/nccl_compress_tools.c", [*nb.cuda_libs(), "-lnccl"]),
         ("libccb_coccl_hooks.so", root / "csrc/wrappers/coccl_hooks.c", [str(dst), *nb.cuda_libs(), *rpath]),
+        # lossless float codec behind the same four hooks (the reference's DietGPU wrapper role)
+        ("libdietgpu_wrapper.so", root / "userconfig/wrapper_code_examples/compression/dietgpu/dietgpu.c",
+         [str(dst), *nb.cuda_libs(), *rpath]),
     ]:
         if src.exists():
             nb.cc(libs / name, [src], shared=True, libs=extra, verbose=verbose)

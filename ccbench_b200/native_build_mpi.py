@@ -32,6 +32,7 @@ def build(verbose: bool = False) -> None:
           libs=shared_link, verbose=verbose, compiler=cc)
     nb.cc(libs / "libmpi_int8.so", [ex / "compression/int8_block/mpi_int8_wrapper.c"], shared=True, libs=["-lm"], verbose=verbose)
     nb.cc(libs / "libmpi_szcpu.so", [ex / "compression/sz_cpu/mpi_szcpu_wrapper.c"], shared=True, libs=["-lm"], verbose=verbose)
-    nb.cc(libs / "libmpi_zfp.so", [ex / "compression/zfp/mpi_zfp_wrapper.c"], shared=True, libs=["-lm"], verbose=verbose)
+    nb.cc(libs / "libmpi_zfp.so", [ex / "compression/zfp/mpi_zfp_wrapper.c"], shared=True, libs=["-lm", "-ldl"], verbose=verbose)
+    nb.cc(libs / "libmpi_sz3.so", [ex / "compression/sz3/mpi_sz3_wrapper.c"], shared=True, libs=["-lm", "-ldl"], verbose=verbose)
     nb.cc(libs / "libperfmpi.so", [ex / "perf/perfmpi/perfmpi.c", root / "csrc/wrappers/perf_helper_mpi.c", root / "csrc/core/perf.c"],
           extra=inc, shared=True, libs=shared_link, verbose=verbose, compiler=cc)

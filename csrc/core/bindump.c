@@ -80,6 +80,14 @@ void binary_accumulate(void *accum, const void *buf, int count, data_type_t dtyp
         case TYPE_INT: for (int i = 0; i < count; ++i) ((int *)accum)[i] += ((const int *)buf)[i]; break;
         case TYPE_FLOAT: for (int i = 0; i < count; ++i) ((float *)accum)[i] += ((const float *)buf)[i]; break;
         case TYPE_DOUBLE: for (int i = 0; i < count; ++i) ((double *)accum)[i] += ((const double *)buf)[i]; break;
+        case TYPE_BFLOAT16:
+            for (int i = 0; i < count; ++i)
+                ((uint16_t *)accum)[i] = ccb_float_to_bf16(ccb_bf16_to_float(((uint16_t *)accum)[i]) + ccb_bf16_to_float(((const uint16_t *)buf)[i]));
+            break;
+        case TYPE_HALF:
+            for (int i = 0; i < count; ++i)
+                ((uint16_t *)accum)[i] = ccb_float_to_half(ccb_half_to_float(((uint16_t *)accum)[i]) + ccb_half_to_float(((const uint16_t *)buf)[i]));
+            break;
         default: for (int i = 0; i < count; ++i) ((char *)accum)[i] = (char)(((char *)accum)[i] + ((const char *)buf)[i]); break;
     }
 }
@@ -90,6 +98,12 @@ void binary_average(void *accum, int count, data_type_t dtype, int divisor) {
         case TYPE_INT: for (int i = 0; i < count; ++i) ((int *)accum)[i] /= divisor; break;
         case TYPE_FLOAT: for (int i = 0; i < count; ++i) ((float *)accum)[i] /= (float)divisor; break;
         case TYPE_DOUBLE: for (int i = 0; i < count; ++i) ((double *)accum)[i] /= (double)divisor; break;
+        case TYPE_BFLOAT16:
+            for (int i = 0; i < count; ++i) ((uint16_t *)accum)[i] = ccb_float_to_bf16(ccb_bf16_to_float(((uint16_t *)accum)[i]) / (float)divisor);
+            break;
+        case TYPE_HALF:
+            for (int i = 0; i < count; ++i) ((uint16_t *)accum)[i] = ccb_float_to_half(ccb_half_to_float(((uint16_t *)accum)[i]) / (float)divisor);
+            break;
         default: for (int i = 0; i < count; ++i) ((char *)accum)[i] = (char)(((char *)accum)[i] / divisor); break;
     }
 }

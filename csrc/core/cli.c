@@ -39,6 +39,11 @@ int read_from_file(const char *filename, void *buffer, size_t buffer_size, file_
             if (datatype == TYPE_INT) ok = fscanf(fp, "%d", (int *)buffer + i);
             else if (datatype == TYPE_FLOAT) ok = fscanf(fp, "%f", (float *)buffer + i);
             else if (datatype == TYPE_DOUBLE) ok = fscanf(fp, "%lf", (double *)buffer + i);
+            else if (datatype == TYPE_BFLOAT16 || datatype == TYPE_HALF) {
+                float f = 0.f;
+                ok = fscanf(fp, "%f", &f);
+                ((uint16_t *)buffer)[i] = datatype == TYPE_HALF ? ccb_float_to_half(f) : ccb_float_to_bf16(f);
+            }
             else {
                 int v;
                 ok = fscanf(fp, "%d", &v);
@@ -69,6 +74,8 @@ int write_to_file(const char *filename, const void *buffer, size_t buffer_size, 
             if (datatype == TYPE_INT) fprintf(fp, "%d\n", ((const int *)buffer)[i]);
             else if (datatype == TYPE_FLOAT) fprintf(fp, "%.9g\n", ((const float *)buffer)[i]);
             else if (datatype == TYPE_DOUBLE) fprintf(fp, "%.17g\n", ((const double *)buffer)[i]);
+            else if (datatype == TYPE_BFLOAT16) fprintf(fp, "%.9g\n", ccb_bf16_to_float(((const uint16_t *)buffer)[i]));
+            else if (datatype == TYPE_HALF) fprintf(fp, "%.9g\n", ccb_half_to_float(((const uint16_t *)buffer)[i]));
             else fprintf(fp, "%d\n", (int)((const char *)buffer)[i]);
         }
     }
@@ -117,6 +124,8 @@ void init_buffer_pattern(void *buffer, int count, data_type_t datatype, pattern_
         if (datatype == TYPE_INT) ((int *)buffer)[i] = iv;
         else if (datatype == TYPE_FLOAT) ((float *)buffer)[i] = (float)iv;
         else if (datatype == TYPE_DOUBLE) ((double *)buffer)[i] = (double)iv;
+        else if (datatype == TYPE_BFLOAT16) ((uint16_t *)buffer)[i] = ccb_float_to_bf16((float)iv);
+        else if (datatype == TYPE_HALF) ((uint16_t *)buffer)[i] = ccb_float_to_half((float)iv);
         else ((char *)buffer)[i] = (char)((rank + i) % 256);
     }
 }
@@ -129,6 +138,8 @@ void print_buffer(const void *buffer, int count, data_type_t datatype, int max_t
         if (datatype == TYPE_INT) printf("%d ", ((const int *)buffer)[i]);
         else if (datatype == TYPE_FLOAT) printf("%.3f ", ((const float *)buffer)[i]);
         else if (datatype == TYPE_DOUBLE) printf("%.6lf ", ((const double *)buffer)[i]);
+        else if (datatype == TYPE_BFLOAT16) printf("%.3f ", ccb_bf16_to_float(((const uint16_t *)buffer)[i]));
+        else if (datatype == TYPE_HALF) printf("%.3f ", ccb_half_to_float(((const uint16_t *)buffer)[i]));
         else printf("%d ", (int)((const char *)buffer)[i]);
     }
     printf("\n");
@@ -237,8 +248,10 @@ test_config_t parse_arguments(int argc, char **argv) {
                 else if (!strcasecmp(optarg, "double")) c.data_type = TYPE_DOUBLE;
                 else if (!strcasecmp(optarg, "int")) c.data_type = TYPE_INT;
                 else if (!strcasecmp(optarg, "char")) c.data_type = TYPE_CHAR;
+                else if (!strcasecmp(optarg, "bfloat16") || !strcasecmp(optarg, "bf16")) c.data_type = TYPE_BFLOAT16;
+                else if (!strcasecmp(optarg, "half") || !strcasecmp(optarg, "float16") || !strcasecmp(optarg, "fp16")) c.data_type = TYPE_HALF;
                 else {
-                    fprintf(stderr, "Unknown data type: '%s' (options: float, double, int, char)\n", optarg);
+                    fprintf(stderr, "Unknown data type: '%s' (options: float, double, int, char, bfloat16, half)\n", optarg);
                     exit(1);
                 }
                 break;
@@ -291,7 +304,8 @@ int size_iter_next(size_iter_t *it, size_t *size) {
 
 /* -------------------------------------------------------------- oracle cache */
 static const char *dtype_tag(data_type_t t) {
-    return t == TYPE_INT ? "int" : t == TYPE_FLOAT ? "float" : t == TYPE_DOUBLE ? "double" : "char";
+    return t == TYPE_INT ? "int" : t == TYPE_FLOAT ? "float" : t == TYPE_DOUBLE ? "double" : t == TYPE_BFLOAT16 ? "bfloat16"
+           : t == TYPE_HALF ? "half" : "char";
 }
 
 static void ref_cache_name(char *out, size_t cap, const char *dir, const test_config_t *cfg, const char *collective,

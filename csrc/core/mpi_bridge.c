@@ -100,7 +100,8 @@ void mpi_load_input(const mpi_test_context_t *ctx, void *buf, size_t msg_size, M
 }
 
 static const char *dtype_name(data_type_t t) {
-    return t == TYPE_INT ? "int" : t == TYPE_FLOAT ? "float" : t == TYPE_DOUBLE ? "double" : "char";
+    return t == TYPE_INT ? "int" : t == TYPE_FLOAT ? "float" : t == TYPE_DOUBLE ? "double" : t == TYPE_BFLOAT16 ? "bfloat16"
+           : t == TYPE_HALF ? "half" : "char";
 }
 
 void mpi_report_results(const mpi_test_context_t *ctx, size_t msg_size, int count, double total_time_user,

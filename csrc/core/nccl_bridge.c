@@ -315,7 +315,8 @@ void nccl_load_input(const nccl_test_context_t *ctx, void *buf, size_t msg_size,
 
 /* ----------------------------------------------------------------- reporting */
 static const char *dtype_name(data_type_t t) {
-    return t == TYPE_INT ? "int" : t == TYPE_FLOAT ? "float" : t == TYPE_DOUBLE ? "double" : "char";
+    return t == TYPE_INT ? "int" : t == TYPE_FLOAT ? "float" : t == TYPE_DOUBLE ? "double" : t == TYPE_BFLOAT16 ? "bfloat16"
+           : t == TYPE_HALF ? "half" : "char";
 }
 
 void nccl_report_results(const nccl_test_context_t *ctx, size_t msg_size, int count, float total_time_ms,
@@ -424,6 +425,10 @@ data_type_t nccl_to_data_type(ncclDataType_t t) {
         case ncclInt32: case ncclUint32: return TYPE_INT;
         case ncclFloat32: return TYPE_FLOAT;
         case ncclFloat64: case ncclInt64: case ncclUint64: return TYPE_DOUBLE; /* 8-byte elements, as the reference maps them */
+        case ncclFloat16: return TYPE_HALF;
+#if defined(__CUDA_BF16_TYPES_EXIST__) || defined(NCCL_BF16_TYPES_EXIST) || NCCL_VERSION_CODE >= 21000
+        case ncclBfloat16: return TYPE_BFLOAT16;
+#endif
         default: return TYPE_CHAR;
     }
 }
@@ -432,6 +437,10 @@ ncclDataType_t data_type_to_nccl(data_type_t t) {
         case TYPE_INT: return ncclInt32;
         case TYPE_FLOAT: return ncclFloat32;
         case TYPE_DOUBLE: return ncclFloat64;
+        case TYPE_HALF: return ncclFloat16;
+#if defined(__CUDA_BF16_TYPES_EXIST__) || defined(NCCL_BF16_TYPES_EXIST) || NCCL_VERSION_CODE >= 21000
+        case TYPE_BFLOAT16: return ncclBfloat16;
+#endif
         default: return ncclInt8;
     }
 }

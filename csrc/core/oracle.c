@@ -109,6 +109,15 @@ static void add_into(void *dst, const void *src, int count, data_type_t t) {
         case TYPE_INT: for (int i = 0; i < count; ++i) ((int *)dst)[i] += ((const int *)src)[i]; break;
         case TYPE_FLOAT: for (int i = 0; i < count; ++i) ((float *)dst)[i] += ((const float *)src)[i]; break;
         case TYPE_DOUBLE: for (int i = 0; i < count; ++i) ((double *)dst)[i] += ((const double *)src)[i]; break;
+        /* element-type accumulation of a 16-bit float: one rounding per addition */
+        case TYPE_BFLOAT16:
+            for (int i = 0; i < count; ++i)
+                ((uint16_t *)dst)[i] = ccb_float_to_bf16(ccb_bf16_to_float(((uint16_t *)dst)[i]) + ccb_bf16_to_float(((const uint16_t *)src)[i]));
+            break;
+        case TYPE_HALF:
+            for (int i = 0; i < count; ++i)
+                ((uint16_t *)dst)[i] = ccb_float_to_half(ccb_half_to_float(((uint16_t *)dst)[i]) + ccb_half_to_float(((const uint16_t *)src)[i]));
+            break;
         default: for (int i = 0; i < count; ++i) ((char *)dst)[i] = (char)(((char *)dst)[i] + ((const char *)src)[i]); break;
     }
 }
@@ -124,6 +133,12 @@ static void *xmalloc(size_t n) {
 
 void dummy_allreduce(void *ref, const char *input_file, data_type_t datatype, pattern_type_t pattern_type, int count,
                      int nranks) {
+    if (datatype == TYPE_BFLOAT16 || datatype == TYPE_HALF) {
+        /* a sum carried in a 16-bit float would be a worse reference than the device's fp32
+         * accumulation: these types are summed in float64 and rounded once */
+        dummy_allreduce_f64(ref, input_file, datatype, pattern_type, count, nranks);
+        return;
+    }
     const size_t bytes = (size_t)count * get_element_size(datatype);
     void *tmp = xmalloc(bytes);
     dummy_load_rank_data(input_file, datatype, pattern_type, ref, bytes, 0, nranks);
@@ -151,6 +166,8 @@ void dummy_allreduce_f64(void *ref, const char *input_file, data_type_t datatype
         if (datatype == TYPE_INT) ((int *)ref)[i] = (int)acc[i];
         else if (datatype == TYPE_FLOAT) ((float *)ref)[i] = (float)acc[i];
         else if (datatype == TYPE_DOUBLE) ((double *)ref)[i] = acc[i];
+        else if (datatype == TYPE_BFLOAT16) ((uint16_t *)ref)[i] = ccb_float_to_bf16((float)acc[i]);
+        else if (datatype == TYPE_HALF) ((uint16_t *)ref)[i] = ccb_float_to_half((float)acc[i]);
         else ((char *)ref)[i] = (char)acc[i];
     }
     free(acc);

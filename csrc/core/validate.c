@@ -72,6 +72,7 @@ size_t get_element_size(data_type_t dtype) {
         case TYPE_INT: return sizeof(int);
         case TYPE_FLOAT: return sizeof(float);
         case TYPE_DOUBLE: return sizeof(double);
+        case TYPE_BFLOAT16: case TYPE_HALF: return 2;
         default: return 1;
     }
 }
@@ -81,6 +82,8 @@ double to_double(const void *ptr, data_type_t dtype, int index) {
         case TYPE_INT: return (double)((const int *)ptr)[index];
         case TYPE_FLOAT: return (double)((const float *)ptr)[index];
         case TYPE_DOUBLE: return ((const double *)ptr)[index];
+        case TYPE_BFLOAT16: return (double)ccb_bf16_to_float(((const uint16_t *)ptr)[index]);
+        case TYPE_HALF: return (double)ccb_half_to_float(((const uint16_t *)ptr)[index]);
         default: return (double)((const char *)ptr)[index];
     }
 }
@@ -97,6 +100,11 @@ int buffers_equal(const void *buf1, const void *buf2, int count, data_type_t dat
         const double *a = (const double *)buf1, *b = (const double *)buf2;
         for (int i = 0; i < count; ++i)
             if (!(fabs(a[i] - b[i]) <= tolerance)) return 0;
+        return 1;
+    }
+    if (datatype == TYPE_BFLOAT16 || datatype == TYPE_HALF) {
+        for (int i = 0; i < count; ++i)
+            if (!(fabs(to_double(buf1, datatype, i) - to_double(buf2, datatype, i)) <= tolerance)) return 0;
         return 1;
     }
     return memcmp(buf1, buf2, (size_t)count * get_element_size(datatype)) == 0;

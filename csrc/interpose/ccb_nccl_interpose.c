@@ -24,6 +24,8 @@
  *                                traffic stays there); one encode kernel before the send and
  *                                one decode kernel after the receive, stream-ordered, no host
  *                                synchronisation, also inside ncclGroupStart/End.
+ *   CCB_NVLS=1                   also map the arenas through an NVLS multicast object (lets the
+ *                                large two-shot kernel broadcast its reduced shard in one store)
  *   CCB_MIN_BYTES=N              smaller messages go to NCCL (default 0)
  *   CCB_VERBOSE=1                log decisions to stderr                         */
 #define _GNU_SOURCE
@@ -51,8 +53,9 @@ typedef struct {
 
 typedef struct {
     ncclComm_t comm;
-    const void *buf;
-    size_t count;
+    const void *buf, *out; /* the call's send and receive buffers: an in-place call and an */
+    size_t count;          /* out-of-place call on the same send buffer keep separate residuals */
+    int kind;              /* 0 = AllReduce, 1 = ReduceScatter */
     float *resid;
     uint64_t last_use;
 } ef_slot;
@@ -151,6 +154,12 @@ REAL(ncclScatter, fn_ext_rooted)
 REAL(ncclGather, fn_ext_rooted)
 
 /* ------------------------------------------------------------ comm set-up --- */
+static int dtype_of(ncclDataType_t t);
+/* bytes of `count` elements, for the CCB_MIN_BYTES test (0 for types the fused path does not take) */
+static size_t bytes_of(size_t count, ncclDataType_t t) {
+    const int d = dtype_of(t);
+    return d < 0 ? 0 : count * (d == CCB_F32 ? 4u : 2u);
+}
 static int dtype_of(ncclDataType_t t) {
     if (t == ncclFloat32) return CCB_F32;
     if (t == ncclFloat16) return CCB_F16;
@@ -248,12 +257,14 @@ static ccb_comm *fused_comm(ncclComm_t comm, ncclDataType_t dt, size_t bytes, cu
     return c;
 }
 
-static float *ef_buffer(ncclComm_t comm, const void *buf, size_t count) {
+static float *ef_buffer(ncclComm_t comm, const void *buf, const void *out, size_t count, int kind) {
     if (!cfg.ef) return NULL;
     pthread_mutex_lock(&g_lock);
     ef_slot *hit = NULL, *victim = &g_ef[0];
     for (int i = 0; i < MAX_EF; ++i) {
-        if (g_ef[i].resid && g_ef[i].comm == comm && g_ef[i].buf == buf && g_ef[i].count == count) hit = &g_ef[i];
+        if (g_ef[i].resid && g_ef[i].comm == comm && g_ef[i].buf == buf && g_ef[i].out == out && g_ef[i].count == count &&
+            g_ef[i].kind == kind)
+            hit = &g_ef[i];
         if (g_ef[i].last_use < victim->last_use) victim = &g_ef[i];
     }
     if (!hit) {
@@ -263,6 +274,8 @@ static float *ef_buffer(ncclComm_t comm, const void *buf, size_t count) {
             cudaMemset(victim->resid, 0, count * sizeof(float)) == cudaSuccess) {
             victim->comm = comm;
             victim->buf = buf;
+            victim->out = out;
+            victim->kind = kind;
             victim->count = count;
             hit = victim;
         } else {
@@ -290,9 +303,9 @@ static int lossy_ok(int codec, ncclRedOp_t op) { return codec == CCB_CODEC_NONE 
 ncclResult_t ncclAllReduce(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op,
                            ncclComm_t comm, cudaStream_t stream) {
     load_cfg();
-    ccb_comm *c = lossy_ok(cfg.codec, op) ? fused_comm(comm, datatype, count * (dtype_of(datatype) == CCB_F32 ? 4 : 2), stream, NULL, NULL) : NULL;
+    ccb_comm *c = lossy_ok(cfg.codec, op) ? fused_comm(comm, datatype, bytes_of(count, datatype), stream, NULL, NULL) : NULL;
     if (c) {
-        float *ef = cfg.codec != CCB_CODEC_NONE ? ef_buffer(comm, sendbuff, count) : NULL;
+        float *ef = cfg.codec != CCB_CODEC_NONE ? ef_buffer(comm, sendbuff, recvbuff, count, 0) : NULL;
         const void *s[1] = {sendbuff};
         void *r[1] = {recvbuff};
         float *e[1] = {ef};
@@ -308,11 +321,15 @@ ncclResult_t ncclAllReduce(const void *sendbuff, void *recvbuff, size_t count, n
 ncclResult_t ncclReduceScatter(const void *sendbuff, void *recvbuff, size_t recvcount, ncclDataType_t datatype,
                                ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream) {
     load_cfg();
-    ccb_comm *c = lossy_ok(cfg.codec, op) ? fused_comm(comm, datatype, recvcount * 2, stream, NULL, NULL) : NULL;
+    int n = 0;
+    ccb_comm *c = lossy_ok(cfg.codec, op) ? fused_comm(comm, datatype, bytes_of(recvcount, datatype), stream, NULL, &n) : NULL;
     if (c) {
+        /* the residual covers the whole send buffer: every rank quantises all n shards */
+        float *ef = cfg.codec != CCB_CODEC_NONE ? ef_buffer(comm, sendbuff, recvbuff, recvcount * (size_t)n, 1) : NULL;
         const void *s[1] = {sendbuff};
         void *r[1] = {recvbuff};
-        int rc = ccb_reduce_scatter(c, s, r, recvcount, dtype_of(datatype), (int)op, cfg.codec, NULL, stream);
+        float *e[1] = {ef};
+        int rc = ccb_reduce_scatter(c, s, r, recvcount, dtype_of(datatype), (int)op, cfg.codec, ef ? e : NULL, stream);
         if (rc != CCB_ERR_UNSUPPORTED && rc != CCB_ERR_CAPACITY) return to_nccl(rc);
     }
     fn_reducescatter f = get_ncclReduceScatter();
@@ -321,7 +338,7 @@ ncclResult_t ncclReduceScatter(const void *sendbuff, void *recvbuff, size_t recv
 
 ncclResult_t ncclAllGather(const void *sendbuff, void *recvbuff, size_t sendcount, ncclDataType_t datatype,
                            ncclComm_t comm, cudaStream_t stream) {
-    ccb_comm *c = fused_comm(comm, datatype, sendcount * 2, stream, NULL, NULL);
+    ccb_comm *c = fused_comm(comm, datatype, bytes_of(sendcount, datatype), stream, NULL, NULL);
     if (c) {
         const void *s[1] = {sendbuff};
         void *r[1] = {recvbuff};
@@ -334,7 +351,7 @@ ncclResult_t ncclAllGather(const void *sendbuff, void *recvbuff, size_t sendcoun
 
 ncclResult_t ncclBroadcast(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, int root,
                            ncclComm_t comm, cudaStream_t stream) {
-    ccb_comm *c = fused_comm(comm, datatype, count * 2, stream, NULL, NULL);
+    ccb_comm *c = fused_comm(comm, datatype, bytes_of(count, datatype), stream, NULL, NULL);
     if (c) {
         const void *s[1] = {sendbuff};
         void *r[1] = {recvbuff};
@@ -353,7 +370,7 @@ ncclResult_t ncclReduce(const void *sendbuff, void *recvbuff, size_t count, nccl
                         int root, ncclComm_t comm, cudaStream_t stream) {
     load_cfg();
     int rank = -1;
-    ccb_comm *c = lossy_ok(cfg.codec, op) ? fused_comm(comm, datatype, count * 2, stream, &rank, NULL) : NULL;
+    ccb_comm *c = lossy_ok(cfg.codec, op) ? fused_comm(comm, datatype, bytes_of(count, datatype), stream, &rank, NULL) : NULL;
     if (c) {
         const void *s[1] = {sendbuff};
         void *r[1] = {recvbuff ? recvbuff : (void *)sendbuff}; /* non-root ranks may pass NULL; it is not written */
@@ -367,7 +384,7 @@ ncclResult_t ncclReduce(const void *sendbuff, void *recvbuff, size_t count, nccl
 /* Extended collectives (signatures of nccl_extensions.h; 0 = success). */
 int ncclAllToAll(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
                  ncclDataType_t recvtype, ncclComm_t comm, cudaStream_t stream) {
-    ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, sendcount * 2, stream, NULL, NULL) : NULL;
+    ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, bytes_of(sendcount, sendtype), stream, NULL, NULL) : NULL;
     if (c) {
         const void *s[1] = {sendbuf};
         void *r[1] = {recvbuf};
@@ -384,7 +401,7 @@ int ncclAllToAll(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype,
 typedef ncclResult_t (*fn_a2a_228)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
 ncclResult_t ncclAlltoAll(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
                           cudaStream_t stream) {
-    ccb_comm *c = fused_comm(comm, datatype, count * 2, stream, NULL, NULL);
+    ccb_comm *c = fused_comm(comm, datatype, bytes_of(count, datatype), stream, NULL, NULL);
     if (c) {
         const void *s[1] = {sendbuff};
         void *r[1] = {recvbuff};
@@ -398,7 +415,7 @@ ncclResult_t ncclAlltoAll(const void *sendbuff, void *recvbuff, size_t count, nc
 
 int ncclScatter(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
                 ncclDataType_t recvtype, int root, ncclComm_t comm, cudaStream_t stream) {
-    ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, sendcount * 2, stream, NULL, NULL) : NULL;
+    ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, bytes_of(sendcount, sendtype), stream, NULL, NULL) : NULL;
     if (c) {
         const void *s[1] = {sendbuf ? sendbuf : recvbuf};
         void *r[1] = {recvbuf};
@@ -411,7 +428,7 @@ int ncclScatter(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, 
 
 int ncclGather(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
                ncclDataType_t recvtype, int root, ncclComm_t comm, cudaStream_t stream) {
-    ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, sendcount * 2, stream, NULL, NULL) : NULL;
+    ccb_comm *c = (sendtype == recvtype && sendcount == recvcount) ? fused_comm(comm, sendtype, bytes_of(sendcount, sendtype), stream, NULL, NULL) : NULL;
     if (c) {
         const void *s[1] = {sendbuf};
         void *r[1] = {recvbuf ? recvbuf : (void *)sendbuf};
@@ -428,15 +445,26 @@ int ncclGather(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, v
  * only records the call and runs it at the outermost ncclGroupEnd, so the decode and the
  * release of the temporaries are deferred to that point as well. Both ends must run with the
  * same setting; the wire size is a function of (codec, dtype, count) only. */
-#define MAX_PENDING 256
 typedef struct {
     void *wire, *user; /* user != NULL: a receive to decode into user */
     size_t count;
     int dtype;
     cudaStream_t stream;
 } p2p_pending;
-static __thread p2p_pending g_pending[MAX_PENDING];
-static __thread int g_npending;
+static __thread p2p_pending *g_pending; /* grows as needed: a full table must never change the wire format */
+static __thread int g_npending, g_pending_cap;
+
+static int pending_push(const p2p_pending *p) {
+    if (g_npending == g_pending_cap) {
+        const int cap = g_pending_cap ? 2 * g_pending_cap : 64;
+        p2p_pending *q = (p2p_pending *)realloc(g_pending, (size_t)cap * sizeof(*q));
+        if (!q) return -1;
+        g_pending = q;
+        g_pending_cap = cap;
+    }
+    g_pending[g_npending++] = *p;
+    return 0;
+}
 
 static ncclResult_t p2p_finish(const p2p_pending *p) {
     ncclResult_t rc = ncclSuccess;
@@ -447,8 +475,9 @@ static ncclResult_t p2p_finish(const p2p_pending *p) {
 static int p2p_wanted(size_t count, ncclDataType_t dt, cudaStream_t stream) {
     load_cfg();
     if (cfg.disabled || cfg.p2p_codec == CCB_CODEC_NONE || dtype_of(dt) < 0 || count == 0) return 0;
-    if (count * (dtype_of(dt) == CCB_F32 ? 4 : 2) < cfg.min_bytes || stream_is_capturing(stream)) return 0;
-    return g_group_depth == 0 || g_npending < MAX_PENDING;
+    /* only values both ends share (codec, type, count) may decide the wire format */
+    if (bytes_of(count, dt) < cfg.min_bytes || stream_is_capturing(stream)) return 0;
+    return 1;
 }
 
 ncclResult_t ncclSend(const void *sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {
@@ -464,8 +493,11 @@ ncclResult_t ncclSend(const void *sendbuff, size_t count, ncclDataType_t datatyp
         return ncclInternalError;
     }
     ncclResult_t rc = f(p.wire, wb, ncclUint8, peer, comm, stream);
-    if (g_group_depth > 0 && rc == ncclSuccess) g_pending[g_npending++] = p;
-    else p2p_finish(&p);
+    if (g_group_depth > 0 && rc == ncclSuccess) {
+        if (pending_push(&p) != 0) return ncclSystemError; /* the wire is leaked rather than freed under NCCL */
+    } else {
+        p2p_finish(&p);
+    }
     return rc;
 }
 
@@ -482,10 +514,7 @@ ncclResult_t ncclRecv(void *recvbuff, size_t count, ncclDataType_t datatype, int
         cudaFreeAsync(p.wire, stream);
         return rc;
     }
-    if (g_group_depth > 0) {
-        g_pending[g_npending++] = p;
-        return ncclSuccess;
-    }
+    if (g_group_depth > 0) return pending_push(&p) == 0 ? ncclSuccess : ncclSystemError;
     return p2p_finish(&p);
 }
 

@@ -19,8 +19,13 @@ namespace ccb {
 
 constexpr int kSaThreads = 256;
 
+// blockIdx.y selects one of several equal chunks: chunk c reads in + c * in_stride elements
+// and writes wire + c * wire_stride bytes, so that a chunked buffer is one launch.
 template <class T, class C>
-__global__ void __launch_bounds__(kSaThreads) encode_kernel(const T* __restrict__ in, size_t count, char* wire, size_t pad) {
+__global__ void __launch_bounds__(kSaThreads) encode_kernel(const T* __restrict__ in, size_t count, char* wire, size_t pad,
+                                                            size_t in_stride, size_t wire_stride) {
+  in += (size_t)blockIdx.y * in_stride;
+  wire += (size_t)blockIdx.y * wire_stride;
   const size_t units = pad / kWarpElems;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -36,7 +41,10 @@ __global__ void __launch_bounds__(kSaThreads) encode_kernel(const T* __restrict_
 
 // MODE 0: out = decode(wire); MODE 1: out += decode(wire)
 template <class T, class C, int MODE>
-__global__ void __launch_bounds__(kSaThreads) decode_kernel(const char* wire, size_t count, T* out, size_t pad) {
+__global__ void __launch_bounds__(kSaThreads) decode_kernel(const char* wire, size_t count, T* out, size_t pad,
+                                                            size_t wire_stride, size_t out_stride) {
+  wire += (size_t)blockIdx.y * wire_stride;
+  out += (size_t)blockIdx.y * out_stride;
   const size_t units = pad / kWarpElems;
   const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -124,30 +132,44 @@ static int sa_grid(size_t units) {
   return (int)(blocks < cap ? blocks : cap);
 }
 
+// Grid of a chunked launch: x covers one chunk (at most `cap` blocks over all chunks), y the chunks.
+static dim3 sa_grid2(size_t units, size_t nchunks) {
+  int gx = sa_grid(units);
+  const size_t cap = 148 * 8;
+  if (nchunks > 1 && (size_t)gx * nchunks > cap) gx = (int)(cap / nchunks > 0 ? cap / nchunks : 1);
+  return dim3((unsigned)gx, (unsigned)nchunks, 1);
+}
+
 template <class T>
-static int encode_t(int codec, const void* in, size_t count, void* wire, size_t pad, cudaStream_t s) {
-  const int g = sa_grid(pad / kWarpElems);
+static int encode_t(int codec, const void* in, size_t count, void* wire, size_t pad, cudaStream_t s, size_t nchunks = 1,
+                    size_t in_stride = 0, size_t wire_stride = 0) {
+  const dim3 g = sa_grid2(pad / kWarpElems, nchunks);
+#define CCB_ENC(C) encode_kernel<T, C><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad, in_stride, wire_stride)
   switch (codec) {
-    case CCB_CODEC_NONE: encode_kernel<T, CodecNone<T>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
-    case CCB_CODEC_INT8: encode_kernel<T, CodecInt8<128>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
-    case CCB_CODEC_INT8_G256: encode_kernel<T, CodecInt8<256>><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
-    case CCB_CODEC_FP8: encode_kernel<T, CodecFp8><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
-    case CCB_CODEC_INT4: encode_kernel<T, CodecInt4><<<g, kSaThreads, 0, s>>>((const T*)in, count, (char*)wire, pad); break;
+    case CCB_CODEC_NONE: CCB_ENC(CodecNone<T>); break;
+    case CCB_CODEC_INT8: CCB_ENC(CodecInt8<128>); break;
+    case CCB_CODEC_INT8_G256: CCB_ENC(CodecInt8<256>); break;
+    case CCB_CODEC_FP8: CCB_ENC(CodecFp8); break;
+    case CCB_CODEC_INT4: CCB_ENC(CodecInt4); break;
     default: return CCB_ERR_UNSUPPORTED;
   }
+#undef CCB_ENC
   return CCB_OK;
 }
 template <class T, int MODE>
-static int decode_t(int codec, const void* wire, size_t count, void* out, size_t pad, cudaStream_t s) {
-  const int g = sa_grid(pad / kWarpElems);
+static int decode_t(int codec, const void* wire, size_t count, void* out, size_t pad, cudaStream_t s, size_t nchunks = 1,
+                    size_t wire_stride = 0, size_t out_stride = 0) {
+  const dim3 g = sa_grid2(pad / kWarpElems, nchunks);
+#define CCB_DEC(C) decode_kernel<T, C, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad, wire_stride, out_stride)
   switch (codec) {
-    case CCB_CODEC_NONE: decode_kernel<T, CodecNone<T>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
-    case CCB_CODEC_INT8: decode_kernel<T, CodecInt8<128>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
-    case CCB_CODEC_INT8_G256: decode_kernel<T, CodecInt8<256>, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
-    case CCB_CODEC_FP8: decode_kernel<T, CodecFp8, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
-    case CCB_CODEC_INT4: decode_kernel<T, CodecInt4, MODE><<<g, kSaThreads, 0, s>>>((const char*)wire, count, (T*)out, pad); break;
+    case CCB_CODEC_NONE: CCB_DEC(CodecNone<T>); break;
+    case CCB_CODEC_INT8: CCB_DEC(CodecInt8<128>); break;
+    case CCB_CODEC_INT8_G256: CCB_DEC(CodecInt8<256>); break;
+    case CCB_CODEC_FP8: CCB_DEC(CodecFp8); break;
+    case CCB_CODEC_INT4: CCB_DEC(CodecInt4); break;
     default: return CCB_ERR_UNSUPPORTED;
   }
+#undef CCB_DEC
   return CCB_OK;
 }
 
@@ -195,6 +217,49 @@ extern "C" int ccb_decode_reduce(int codec, int dtype, const void* wire, uint64_
            : dtype == CCB_F16  ? decode_t<__half, 1>(codec, wire, count, inout, pad_of(count), s)
                                : CCB_ERR_UNSUPPORTED;
   return rc ? rc : finish("ccb_decode_reduce");
+}
+
+// The same three operations on `nchunks` equal chunks in ONE launch: chunk c holds
+// chunk_count elements at element offset c * chunk_count of the plain buffer and its wire at
+// byte offset c * wire_stride (wire_stride >= ccb_wire_bytes(codec, dtype, chunk_count), a
+// multiple of 16). chunk_count must keep every chunk 16-byte aligned for the fast path;
+// other counts work through the element-wise path.
+extern "C" int ccb_encode_chunks(int codec, int dtype, const void* in, uint64_t chunk_count, uint64_t nchunks, void* wire,
+                                 uint64_t wire_stride, void* stream) {
+  if (!chunk_count || !nchunks) return CCB_OK;
+  if (nchunks > 65535) {
+    set_error("at most 65535 chunks per call");
+    return CCB_ERR_ARG;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t pad = pad_of(chunk_count);
+  int rc = dtype == CCB_F32    ? encode_t<float>(codec, in, chunk_count, wire, pad, s, nchunks, chunk_count, wire_stride)
+           : dtype == CCB_BF16 ? encode_t<__nv_bfloat16>(codec, in, chunk_count, wire, pad, s, nchunks, chunk_count, wire_stride)
+           : dtype == CCB_F16  ? encode_t<__half>(codec, in, chunk_count, wire, pad, s, nchunks, chunk_count, wire_stride)
+                               : CCB_ERR_UNSUPPORTED;
+  return rc ? rc : finish("ccb_encode_chunks");
+}
+extern "C" int ccb_decode_chunks(int codec, int dtype, const void* wire, uint64_t wire_stride, uint64_t chunk_count,
+                                 uint64_t nchunks, void* out, int accumulate, void* stream) {
+  if (!chunk_count || !nchunks) return CCB_OK;
+  if (nchunks > 65535) {
+    set_error("at most 65535 chunks per call");
+    return CCB_ERR_ARG;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t pad = pad_of(chunk_count);
+  int rc;
+  if (accumulate)
+    rc = dtype == CCB_F32    ? decode_t<float, 1>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
+         : dtype == CCB_BF16 ? decode_t<__nv_bfloat16, 1>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
+         : dtype == CCB_F16  ? decode_t<__half, 1>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
+                             : CCB_ERR_UNSUPPORTED;
+  else
+    rc = dtype == CCB_F32    ? decode_t<float, 0>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
+         : dtype == CCB_BF16 ? decode_t<__nv_bfloat16, 0>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
+         : dtype == CCB_F16  ? decode_t<__half, 0>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
+                             : CCB_ERR_UNSUPPORTED;
+  return rc ? rc : finish("ccb_decode_chunks");
 }
 
 extern "C" int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out, void* stream) {

@@ -36,7 +36,6 @@ static int hook_dtype(ncclDataType_t t) {
     if ((int)t == 9) return CCB_BF16;
     return -1;
 }
-static size_t esz(int dt) { return dt == CCB_F32 ? 4 : 2; }
 
 /* Bytes one compressed chunk occupies (the fixed stride between chunks). */
 size_t ncclCompressedChunkBytes(size_t chunkCount, ncclDataType_t datatype) {
@@ -57,11 +56,9 @@ ncclResult_t ncclCompress(const void *orgbuff, void **compbuff, const size_t org
     *compDatatype = ncclUint8;
     *compChunkCount = stride;
     if (*compbuff == NULL && cudaMallocAsync(compbuff, stride * numChunks, stream) != cudaSuccess) return ncclInternalError;
-    for (size_t c = 0; c < numChunks; ++c)
-        if (ccb_encode(hook_codec(), dt, (const char *)orgbuff + c * orgChunkCount * esz(dt), orgChunkCount,
-                       (char *)*compbuff + c * stride, stream))
-            return ncclInternalError;
-    return ncclSuccess;
+    /* all chunks in one launch (the reference's template launches per chunk, :74-100) */
+    return ccb_encode_chunks(hook_codec(), dt, orgbuff, orgChunkCount, numChunks, *compbuff, stride, stream) ? ncclInternalError
+                                                                                                           : ncclSuccess;
 }
 
 ncclResult_t ncclDecompress(void *decompbuff, const void *compbuff, const size_t decompChunkCount,
@@ -71,14 +68,12 @@ ncclResult_t ncclDecompress(void *decompbuff, const void *compbuff, const size_t
     (void)commOp;
     const int dt = hook_dtype(decompDatatype);
     if (dt < 0) return ncclInternalError;
-    for (size_t c = 0; c < numChunks; ++c)
-        if (ccb_decode(hook_codec(), dt, (const char *)compbuff + c * compChunkCount, decompChunkCount,
-                       (char *)decompbuff + c * decompChunkCount * esz(dt), stream))
-            return ncclInternalError;
-    return ncclSuccess;
+    return ccb_decode_chunks(hook_codec(), dt, compbuff, compChunkCount, decompChunkCount, numChunks, decompbuff, 0, stream)
+               ? ncclInternalError
+               : ncclSuccess;
 }
 
-/* reducebuff[c] += decode(compbuff[c]) for every chunk, one kernel per chunk. */
+/* reducebuff[c] += decode(compbuff[c]) for every chunk, one kernel for all chunks. */
 ncclResult_t ncclDecompressReduce(void *reducebuff, const void *compbuff, const size_t compChunkCount,
                                   ncclDataType_t compDatatype, const size_t reduceChunkCount, ncclDataType_t reduceDataType,
                                   const size_t numChunks, ncclCommOp_t commOp, cudaStream_t stream) {
@@ -86,11 +81,9 @@ ncclResult_t ncclDecompressReduce(void *reducebuff, const void *compbuff, const 
     (void)commOp;
     const int dt = hook_dtype(reduceDataType);
     if (dt < 0) return ncclInternalError;
-    for (size_t c = 0; c < numChunks; ++c)
-        if (ccb_decode_reduce(hook_codec(), dt, (const char *)compbuff + c * compChunkCount, reduceChunkCount,
-                              (char *)reducebuff + c * reduceChunkCount * esz(dt), stream))
-            return ncclInternalError;
-    return ncclSuccess;
+    return ccb_decode_chunks(hook_codec(), dt, compbuff, compChunkCount, reduceChunkCount, numChunks, reducebuff, 1, stream)
+               ? ncclInternalError
+               : ncclSuccess;
 }
 
 /* *recompbuff = encode(sum over the numChunks compressed chunks): one chunk out. */

@@ -104,6 +104,14 @@ int ccb_encode(int codec, int dtype, const void* in, uint64_t count, void* wire,
 int ccb_decode(int codec, int dtype, const void* wire, uint64_t count, void* out, ccb_stream_t stream);
 /* inout += decode(wire) */
 int ccb_decode_reduce(int codec, int dtype, const void* wire, uint64_t count, void* inout, ccb_stream_t stream);
+/* The same on `nchunks` equal chunks in ONE launch: chunk c is chunk_count elements at
+ * element offset c * chunk_count of the plain buffer, its wire at byte offset
+ * c * wire_stride (>= ccb_wire_bytes(codec, dtype, chunk_count), a multiple of 16).
+ * accumulate != 0: out[c] += decode(wire[c]). */
+int ccb_encode_chunks(int codec, int dtype, const void* in, uint64_t chunk_count, uint64_t nchunks, void* wire,
+                      uint64_t wire_stride, ccb_stream_t stream);
+int ccb_decode_chunks(int codec, int dtype, const void* wire, uint64_t wire_stride, uint64_t chunk_count, uint64_t nchunks,
+                      void* out, int accumulate, ccb_stream_t stream);
 /* wire_out = encode(sum_k decode(wires[k])), 1 <= nwires <= 16 */
 int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out,
                       ccb_stream_t stream);

@@ -12,7 +12,52 @@
 extern "C" {
 #endif
 
-typedef enum { TYPE_INT, TYPE_FLOAT, TYPE_DOUBLE, TYPE_CHAR } data_type_t;
+/* The reference has the first four (run_codes/benchmark-core/include/utils.h:13-18); the
+ * 16-bit floating types are additions, appended so that the reference's values keep
+ * their numbers. `-d bfloat16` (bf16) and `-d half` (float16, fp16) select them. */
+typedef enum { TYPE_INT, TYPE_FLOAT, TYPE_DOUBLE, TYPE_CHAR, TYPE_BFLOAT16, TYPE_HALF } data_type_t;
+
+/* 16-bit floats on the host: stored as their bit patterns, converted with round to
+ * nearest even, NaN kept. */
+static inline float ccb_bf16_to_float(uint16_t h) {
+    union { uint32_t u; float f; } v;
+    v.u = (uint32_t)h << 16;
+    return v.f;
+}
+static inline uint16_t ccb_float_to_bf16(float f) {
+    union { uint32_t u; float f; } v;
+    v.f = f;
+    if ((v.u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((v.u >> 16) | 0x40u); /* NaN */
+    return (uint16_t)((v.u + 0x7fffu + ((v.u >> 16) & 1u)) >> 16);
+}
+static inline float ccb_half_to_float(uint16_t h) {
+    union { uint32_t u; float f; } v;
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+    if (exp == 0x1fu) v.u = sign | 0x7f800000u | (man << 13);
+    else if (exp) v.u = sign | ((exp + 112u) << 23) | (man << 13);
+    else if (man) {
+        int e = -1;
+        uint32_t m = man;
+        do { ++e; m <<= 1; } while (!(m & 0x400u));
+        v.u = sign | ((uint32_t)(112 - e) << 23) | ((m & 0x3ffu) << 13);
+    } else v.u = sign;
+    return v.f;
+}
+static inline uint16_t ccb_float_to_half(float f) {
+    union { uint32_t u; float f; } v;
+    v.f = f;
+    const uint32_t sign = (v.u >> 16) & 0x8000u, a = v.u & 0x7fffffffu;
+    if (a > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);                 /* NaN */
+    if (a >= 0x477ff000u) return (uint16_t)(sign | 0x7c00u);                /* rounds to infinity */
+    if (a < 0x33000001u) return (uint16_t)sign;                             /* rounds to zero */
+    if (a < 0x38800000u) {                                                  /* subnormal half */
+        const uint32_t shift = 126u - (a >> 23), m = (a & 0x7fffffu) | 0x800000u;
+        const uint32_t q = m >> shift, rem = m & ((1u << shift) - 1u), half = 1u << (shift - 1);
+        return (uint16_t)(sign | (q + (rem > half || (rem == half && (q & 1u)))));
+    }
+    const uint32_t q = (a - 0x38000000u) >> 13, rem = a & 0x1fffu;
+    return (uint16_t)(sign | (q + (rem > 0x1000u || (rem == 0x1000u && (q & 1u)))));
+}
 
 typedef enum {
     PATTERN_PLAIN = 0,        /* every element 1                  */

@@ -290,3 +290,89 @@ def test_device_map_csv(tmp_path, monkeypatch):
     lib.device_map_init(ctx, 0, 1)
     lib.map_job_to_device(ctx)  # dispatcher: cpu mapper adds the affinity set
     assert struct.unpack_from("i", ctx.raw, 8 + 4096 * 88)[0] >= 0
+
+
+# ------------------------------------------------------------ 16-bit float types --
+# helper library: the header's inline conversions made callable
+_HALF_SRC = r'''
+#include "utils.h"
+unsigned short t_f2bf(float f) { return ccb_float_to_bf16(f); }
+float t_bf2f(unsigned short h) { return ccb_bf16_to_float(h); }
+unsigned short t_f2h(float f) { return ccb_float_to_half(f); }
+float t_h2f(unsigned short h) { return ccb_half_to_float(h); }
+'''
+
+
+@pytest.fixture(scope="session")
+def halfconv(tmp_path_factory):
+    d = tmp_path_factory.mktemp("half")
+    (d / "h.c").write_text(_HALF_SRC)
+    so = d / "libhalf.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-O2", f"-I{ROOT}/include/ccb/compat", str(d / "h.c"), "-o", str(so)], check=True)
+    L = ctypes.CDLL(str(so))
+    for f, a, r in (("t_f2bf", ctypes.c_float, ctypes.c_ushort), ("t_bf2f", ctypes.c_ushort, ctypes.c_float),
+                    ("t_f2h", ctypes.c_float, ctypes.c_ushort), ("t_h2f", ctypes.c_ushort, ctypes.c_float)):
+        getattr(L, f).argtypes, getattr(L, f).restype = [a], r
+    return L
+
+
+def test_half_and_bfloat16_conversions_match_numpy_and_torch(halfconv):
+    import torch
+
+    rng = np.random.default_rng(0)
+    vals = np.concatenate([rng.standard_normal(2000).astype(np.float32) * 10.0 ** rng.integers(-9, 6, 2000),
+                           np.array([0.0, -0.0, 1.0, 65504.0, 65520.0, 65519.9, 6e-8, 2.98e-8, 5.96e-8, 6.1e-5, 6.0e-5, 1e-10,
+                                     np.inf, -np.inf, 1.0009765625, 1.00048828125, 1.001464843750], dtype=np.float32)])
+    want_h = vals.astype(np.float16).view(np.uint16)
+    want_b = torch.from_numpy(vals).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    for v, wh, wb in zip(vals, want_h, want_b):
+        assert halfconv.t_f2h(float(v)) == int(wh), (float(v), hex(halfconv.t_f2h(float(v))), hex(int(wh)))
+        assert halfconv.t_f2bf(float(v)) == int(wb), float(v)
+    for bits in list(range(0, 0x10000, 37)) + [0x7c00, 0xfc00, 0x0001, 0x03ff, 0x0400, 0x8001]:
+        a = halfconv.t_h2f(bits)
+        b = float(np.array([bits], dtype=np.uint16).view(np.float16)[0])
+        assert (math.isnan(a) and math.isnan(b)) or a == b, hex(bits)
+        c = halfconv.t_bf2f(bits)
+        d = float(torch.tensor([bits], dtype=torch.uint16).view(torch.bfloat16).float()[0])
+        assert (math.isnan(c) and math.isnan(d)) or c == d, hex(bits)
+    assert halfconv.t_f2h(float("nan")) & 0x7c00 == 0x7c00 and halfconv.t_f2h(float("nan")) & 0x3ff
+    assert halfconv.t_f2bf(float("nan")) & 0x7f80 == 0x7f80 and halfconv.t_f2bf(float("nan")) & 0x7f
+
+
+@pytest.mark.parametrize("name,code,npconv", [("bfloat16", 4, None), ("half", 5, np.float16)])
+def test_sixteen_bit_types_through_the_core(core, name, code, npconv):
+    import torch
+
+    c = _parse(core, "-d", name)
+    assert c.data_type == code
+    assert _parse(core, "-d", "bf16").data_type == 4 and _parse(core, "-d", "fp16").data_type == 5
+    core.get_element_size.restype = ctypes.c_size_t
+    assert core.get_element_size(code) == 2
+    n = 300
+    buf = (ctypes.c_uint16 * n)()
+    core.init_buffer_pattern(buf, n, code, 2, 3)  # rank_product, rank 3: 4 * (i + 1)
+    core.to_double.restype = ctypes.c_double
+    core.to_double.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    got = np.array([core.to_double(buf, code, i) for i in range(n)])
+    exact = torch.arange(1, n + 1, dtype=torch.float32) * 4
+    want = exact.to(torch.bfloat16 if code == 4 else torch.float16).double().numpy()
+    assert np.array_equal(got, want)
+    # the all-reduce oracle of a 16-bit type sums in float64 and rounds once
+    ref = (ctypes.c_uint16 * n)()
+    core.dummy_allreduce(ref, None, code, 1, n, 4)  # rank_linear on 4 ranks: sum_r (r + i)
+    ranks = [torch.arange(n, dtype=torch.float32) + r for r in range(4)]
+    tdt = torch.bfloat16 if code == 4 else torch.float16
+    want = sum(x.to(tdt).double() for x in ranks).to(tdt).double().numpy()
+    got = np.array([core.to_double(ref, code, i) for i in range(n)])
+    assert np.array_equal(got, want)
+    # metrics and the tolerance compare see the converted values
+    core.buffers_equal.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_double]
+    other = (ctypes.c_uint16 * n)(*list(ref))
+    other[5] = other[5] + 1   # one ulp off
+    assert core.buffers_equal(ref, ref, n, code, 0.0) == 1
+    assert core.buffers_equal(ref, other, n, code, 0.0) == 0
+    assert core.buffers_equal(ref, other, n, code, 1.0) == 1
+    core.compute_max_abs_err.restype = ctypes.c_double
+    core.compute_max_abs_err.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+    err = core.compute_max_abs_err(other, ref, n, code)
+    assert 0 < err <= 1.0

@@ -114,3 +114,27 @@ def test_fused_hook_library_round_trip():
     torch.cuda.synchronize()
     total = want.view(chunks, per).sum(0)
     assert (one.cpu() - total).abs().max().item() <= 0.51 / 127 * total.abs().max().item() * 1.05
+
+
+def test_all_chunks_of_a_hook_call_are_one_launch():
+    """An 8-chunk ring step is one kernel per hook, not one per chunk, also with a chunk
+    size that is not a multiple of the 512-element wire unit."""
+    L = _load("libccb_coccl_hooks.so")
+    core = ctypes.CDLL(str(LIBS / "libccb.so"))   # the copy the hook library is linked against
+    core.ccb_launch_count.restype = ctypes.c_uint64
+    launch_count = core.ccb_launch_count
+    chunks, per = 8, 3000
+    x = torch.randn(chunks * per, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).cuda()
+    torch.cuda.synchronize()
+    n0 = launch_count()
+    comp, stride, per = _compress(L, x, chunks)
+    assert launch_count() - n0 == 1
+    out = torch.empty_like(x)
+    assert L.ncclDecompress(out.data_ptr(), comp.data_ptr(), per, NCCL_BF16, stride, NCCL_U8, chunks, 2, _stream()) == 0
+    acc = torch.ones_like(x)
+    assert L.ncclDecompressReduce(acc.data_ptr(), comp.data_ptr(), stride, NCCL_U8, per, NCCL_BF16, chunks, 2, _stream()) == 0
+    assert launch_count() - n0 == 3
+    torch.cuda.synchronize()
+    want = torch.cat([C.roundtrip(x.cpu()[c * per:(c + 1) * per], "int8") for c in range(chunks)])
+    assert torch.equal(out.cpu().float(), want.float())
+    assert torch.equal(acc.cpu(), (want.float() + 1).to(torch.bfloat16))

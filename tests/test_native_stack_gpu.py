@@ -91,3 +91,29 @@ def test_compressed_point_to_point_under_the_interposer(tmp_path, test):
     assert max(rel) < 0.02, rel
     if test == "allgatherv":
         assert max(rel) > 0, "the receive path was not compressed"
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "half"])
+def test_sixteen_bit_types_through_the_driver_and_the_interposer(tmp_path, dtype):
+    """`-d bfloat16` / `-d half`: pattern fill, float64 oracle, metrics and the fused kernels."""
+    args = ["-L", "8192,4194304", "-i", "2", "-w", "1", "-d", dtype, "-p", "rank_product", "-v", "-t", "1e30",
+            "-e", "rel_l2,max_abs_err,psnr"]
+    bare = _run(tmp_path, "allreduce", args)
+    assert max(_metric(bare, "rel_l2")) < 5e-3          # NCCL's own 16-bit result against the float64 sum
+    fused = _run(tmp_path, "allreduce", args, preload=["libccb_nccl.so"], env={"CCB_CODEC": "int8", "CCB_VERBOSE": "1"})
+    assert "[ccb_nccl]" in fused and "using NCCL" not in fused, fused[-1500:]
+    assert 0 < max(_metric(fused, "rel_l2")) < 0.03
+    assert _metric(fused, "psnr") and _metric(fused, "max_abs_err")
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="point-to-point needs two GPUs")
+@pytest.mark.parametrize("test", ["pingpong", "overlap"])
+def test_point_to_point_drivers_under_the_interposer(tmp_path, test):
+    """The two drivers that only send and receive: plain under the interposer (NCCL moves the
+    bytes untouched), and the ping-pong again with un-grouped sends and receives compressed."""
+    args = ["-L", "1048576", "-i", "3", "-w", "1", "-d", "float"]
+    out = _run(tmp_path, test, args, preload=["libccb_nccl.so"], env={"CCB_VERBOSE": "1"})
+    assert "Test Complete" in out or "===" in out, out[-1500:]
+    if test == "pingpong":
+        packed = _run(tmp_path, test, args, preload=["libccb_nccl.so"], env={"CCB_P2P_CODEC": "int8"})
+        assert "Test Complete" in packed or "===" in packed, packed[-1500:]

@@ -30,6 +30,13 @@
                     BODY;                                                               \
                 }                                                                       \
                 break;                                                                  \
+            case TYPE_BFLOAT16:                                                         \
+            case TYPE_HALF:                                                             \
+                for (int i_ = 0; i_ < (count); ++i_) {                                  \
+                    const double A = to_double((buf1), (dtype), i_), B = to_double((buf2), (dtype), i_); \
+                    BODY;                                                               \
+                }                                                                       \
+                break;                                                                  \
             default:                                                                    \
                 for (int i_ = 0; i_ < (count); ++i_) {                                  \
                     const double A = ((const char *)(buf1))[i_], B = ((const char *)(buf2))[i_]; \

@@ -22,10 +22,11 @@ static int is_double(void) {
     return e && !strcasecmp(e, "double");
 }
 
-int mpi_compress(void *input, size_t input_size, void *output, size_t *output_size) {
-    const int dbl = is_double();
+/* The codec with explicit parameters (absolute bound, element type); the hooks below and
+ * the SZ3 wrapper's fall-back path call it. */
+static int szcpu_compress(void *input, size_t input_size, void *output, size_t *output_size, double eb, int dbl) {
     const size_t es = dbl ? 8 : 4, n = input_size / es;
-    const double step = 2.0 * abs_eb() * (1.0 - 1.0 / 1024.0);
+    const double step = 2.0 * eb * (1.0 - 1.0 / 1024.0);
     unsigned char *out = (unsigned char *)output, *p = out + 12;
     const unsigned char *end = out + *output_size;
     if (*output_size < 12) return 1;
@@ -64,8 +65,7 @@ int mpi_compress(void *input, size_t input_size, void *output, size_t *output_si
     return 0;
 }
 
-int mpi_decompress(void *input, size_t input_size, void *output, size_t output_size) {
-    const int dbl = is_double();
+static int szcpu_decompress(void *input, size_t input_size, void *output, size_t output_size, int dbl) {
     const size_t es = dbl ? 8 : 4;
     if (input_size < 12) return 1;
     const unsigned char *in = (const unsigned char *)input, *p = in + 12, *end = in + input_size;
@@ -100,3 +100,12 @@ int mpi_decompress(void *input, size_t input_size, void *output, size_t output_s
     if (tail && p + tail <= end) memcpy((char *)output + n * es, p, tail);
     return 0;
 }
+
+#ifndef SZCPU_NO_HOOKS
+int mpi_compress(void *input, size_t input_size, void *output, size_t *output_size) {
+    return szcpu_compress(input, input_size, output, output_size, abs_eb(), is_double());
+}
+int mpi_decompress(void *input, size_t input_size, void *output, size_t output_size) {
+    return szcpu_decompress(input, input_size, output, output_size, is_double());
+}
+#endif
