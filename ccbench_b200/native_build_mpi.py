@@ -28,8 +28,13 @@ def build(verbose: bool = False) -> None:
     shared_link = [l for l in link if not l.startswith("-Wl,-rpath,$ORIGIN/../../libs")]
     nb.cc(libs / "libplain_mpi_compress.so", [ex / "communication/plain_mpi_compress/plain_mpi_compress.c", tools], extra=inc,
           shared=True, libs=shared_link, verbose=verbose, compiler=cc)
-    nb.cc(libs / "libmpi_zccl_wrapper.so", [ex / "communication/zccl/mpi_zccl_wrapper.c", ex / "communication/plain_mpi_compress/plain_mpi_compress.c", tools], extra=inc, shared=True,
+    nb.cc(libs / "libmpi_zccl_wrapper.so", [ex / "communication/zccl/mpi_zccl_wrapper.c", tools], extra=inc, shared=True,
           libs=shared_link, verbose=verbose, compiler=cc)
+    # ZCCL codec replacements and the ZCCL perf wrapper
+    nb.cc(libs / "libsz3_for_zccl.so", [ex / "compression/sz3_for_zccl/sz3_for_zccl.c"], shared=True, libs=["-lm", "-ldl"], verbose=verbose)
+    nb.cc(libs / "libzfp_for_zccl.so", [ex / "compression/zfp_for_zccl/zfp_for_zccl.c"], shared=True, libs=["-lm", "-ldl"], verbose=verbose)
+    nb.cc(libs / "libperfzccl.so", [ex / "perf/perfzccl/perfzccl.c", root / "csrc/wrappers/perf_helper_mpi.c", root / "csrc/core/perf.c"],
+          extra=inc, shared=True, libs=shared_link, verbose=verbose, compiler=cc)
     nb.cc(libs / "libmpi_int8.so", [ex / "compression/int8_block/mpi_int8_wrapper.c"], shared=True, libs=["-lm"], verbose=verbose)
     nb.cc(libs / "libmpi_szcpu.so", [ex / "compression/sz_cpu/mpi_szcpu_wrapper.c"], shared=True, libs=["-lm"], verbose=verbose)
     nb.cc(libs / "libmpi_zfp.so", [ex / "compression/zfp/mpi_zfp_wrapper.c"], shared=True, libs=["-lm", "-ldl"], verbose=verbose)

@@ -60,13 +60,9 @@ static sz3_cfg config(void) {
     return c;
 }
 
-int mpi_compress(void *input, size_t input_size, void *output, size_t *output_size) {
-    if (!input || !output || !output_size) return -1;
-    if (input_size == 0) {
-        *output_size = 0;
-        return 0;
-    }
-    const sz3_cfg c = config();
+/* The codec with explicit parameters: the hooks below call it with the environment's
+ * configuration, the ZCCL codec variant (../sz3_for_zccl) with the bound ZCCL passes. */
+static int sz3_encode(sz3_cfg c, void *input, size_t input_size, void *output, size_t *output_size) {
     const size_t es = c.dbl ? 8 : 4, n = input_size / es;
     if (n == 0) return -1;
     if (have_library()) {
@@ -94,10 +90,7 @@ int mpi_compress(void *input, size_t input_size, void *output, size_t *output_si
     return szcpu_compress(input, input_size, output, output_size, eb, c.dbl);
 }
 
-int mpi_decompress(void *input, size_t input_size, void *output, size_t output_size) {
-    if (!input || !output) return -1;
-    if (input_size == 0 || output_size == 0) return 0;
-    const sz3_cfg c = config();
+static int sz3_decode(sz3_cfg c, void *input, size_t input_size, void *output, size_t output_size) {
     if (have_library()) {
         const size_t n = output_size / (c.dbl ? 8 : 4);
         void *vals = lib_decompress(c.dbl ? 1 : 0, (unsigned char *)input, input_size, 0, 0, 0, 0, n);
@@ -108,3 +101,19 @@ int mpi_decompress(void *input, size_t input_size, void *output, size_t output_s
     }
     return szcpu_decompress(input, input_size, output, output_size, c.dbl);
 }
+
+#ifndef SZ3_NO_HOOKS
+int mpi_compress(void *input, size_t input_size, void *output, size_t *output_size) {
+    if (!input || !output || !output_size) return -1;
+    if (input_size == 0) {
+        *output_size = 0;
+        return 0;
+    }
+    return sz3_encode(config(), input, input_size, output, output_size);
+}
+int mpi_decompress(void *input, size_t input_size, void *output, size_t output_size) {
+    if (!input || !output) return -1;
+    if (input_size == 0 || output_size == 0) return 0;
+    return sz3_decode(config(), input, input_size, output, output_size);
+}
+#endif

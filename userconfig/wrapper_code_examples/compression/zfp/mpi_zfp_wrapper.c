@@ -272,14 +272,9 @@ static int builtin_decompress(void *input, size_t input_size, void *output, size
     return 0;
 }
 
-/* ------------------------------------------------------------------------- hooks -- */
-int mpi_compress(void *input, size_t input_size, void *output, size_t *output_size) {
-    if (!input || !output || !output_size) return -1;
-    if (input_size == 0) {
-        *output_size = 0;
-        return 0;
-    }
-    const zcfg c = config();
+/* The codec with an explicit configuration (the hooks pass the environment's, the ZCCL
+ * codec variant ../zfp_for_zccl the tolerance ZCCL asks for). */
+static int zfp_encode(zcfg c, void *input, size_t input_size, void *output, size_t *output_size) {
     if (c.mode < 1 || c.mode > 5) return -1;
     if (have_library()) {
         const size_t n = input_size / (c.dbl ? 8 : 4);
@@ -298,14 +293,26 @@ int mpi_compress(void *input, size_t input_size, void *output, size_t *output_si
     }
     return builtin_compress(&c, input, input_size, output, output_size);
 }
-
-int mpi_decompress(void *input, size_t input_size, void *output, size_t output_size) {
-    if (!input || !output) return -1;
-    if (input_size == 0 || output_size == 0) return 0;
-    const zcfg c = config();
+static int zfp_decode(zcfg c, void *input, size_t input_size, void *output, size_t output_size) {
     if (have_library()) {
         const size_t n = output_size / (c.dbl ? 8 : 4);
         return (n && lib_run(1, input, input_size, output, n, &c) > 0) ? 0 : -1;
     }
     return builtin_decompress(input, input_size, output, output_size);
 }
+
+#ifndef ZFP_NO_HOOKS
+int mpi_compress(void *input, size_t input_size, void *output, size_t *output_size) {
+    if (!input || !output || !output_size) return -1;
+    if (input_size == 0) {
+        *output_size = 0;
+        return 0;
+    }
+    return zfp_encode(config(), input, input_size, output, output_size);
+}
+int mpi_decompress(void *input, size_t input_size, void *output, size_t output_size) {
+    if (!input || !output) return -1;
+    if (input_size == 0 || output_size == 0) return 0;
+    return zfp_decode(config(), input, input_size, output, output_size);
+}
+#endif
