@@ -79,7 +79,7 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        comm = Communicator.from_torch_distributed(nvls=True)
+        comm = Communicator.from_torch_distributed(nvls=(args.algo == "nvls"))
     else:
         comm = Communicator.create(0, 1, f"bench{os.getpid()}")
 

@@ -188,17 +188,19 @@ def config5(comm, rank, world, dev, args):
     t_comp = _timed(compute_only, 3, 1, world, dev)
     # The collective kernel is one co-resident grid: with every SM taken it starves the GEMMs
     # it should hide behind, so the grid is capped and the cap swept (0 = no cap).
-    for cap in (0, 64, 32, 16):
+    for cap, plain in ((0, False), (64, False), (32, False), (32, True), (16, True), (8, True)):
         comm.set_max_ctas(cap)
+        comm.set_noncooperative(cap if plain else 0)
         t_comm = _timed(comm_only, 3, 1, world, dev)
         t_both = _timed(lambda: both(comm_only), 3, 1, world, dev)
         assert comm.status()[0] == 0
         _emit(rank, {"config": 5, "op": "reduce_scatter buckets", "codec": "int8", "n": world, "buckets": nb, "bucket_bytes": bucket * 2,
-                     "max_ctas": cap, "comm_alone_us": round(t_comm, 1), "compute_alone_us": round(t_comp, 1),
+                     "max_ctas": cap, "launch": "plain" if plain else "cooperative", "comm_alone_us": round(t_comm, 1), "compute_alone_us": round(t_comp, 1),
                      "overlapped_us": round(t_both, 1), "busbw_GBs": round(bucket * 2 * nb / t_comm / 1e3 * fa, 2),
                      "exposed_comm_us": round(t_both - t_comp, 1),
                      "overlap_efficiency": round((t_comm + t_comp - t_both) / min(t_comm, t_comp), 3)})
     comm.set_max_ctas(0)
+    comm.set_noncooperative(0)
     if world > 1:
         t_nccl = _timed(nccl_only, 3, 1, world, dev)
         t_both = _timed(lambda: both(nccl_only), 3, 1, world, dev)

@@ -20,7 +20,7 @@ _DTYPE_FLAG = {"bf16": "bfloat16", "f16": "half", "f32": "float"}
 
 
 def run(x, *, rank: int, world: int, local_rank: int, nbytes: int, dtype: str, codec: str, algo: str, steps: int,
-        warmup: int, nvls: bool = True, validate: bool = True) -> dict | None:
+        warmup: int, nvls: bool = False, validate: bool = True) -> dict | None:
     """`x` is this rank's input tensor (its bytes become the driver's per-rank data file).
     Returns a dict on rank 0, None elsewhere."""
     import torch
@@ -30,8 +30,12 @@ def run(x, *, rank: int, world: int, local_rank: int, nbytes: int, dtype: str, c
 
     exe = ROOT / "bin" / "nccl" / "allreduce" / "allreduce"
     libs = ROOT / "bin" / "libs"
-    if rank == 0 and not (exe.exists() and (libs / "libccb_nccl.so").exists()):
-        build_c_targets()
+    if rank == 0:
+        if not (exe.exists() and (libs / "libccb_nccl.so").exists()):
+            build_c_targets()
+        from ..wrapper_build import register_metrics
+
+        register_metrics()   # bin/libs/validation.so from the current metric sources
     dist.barrier()
     port = os.environ.get("MASTER_PORT", "0")
     run_dir = Path(f"/tmp/ccb_via_{port}")

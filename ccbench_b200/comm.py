@@ -104,12 +104,19 @@ class Communicator:
     def set_max_ctas(self, ctas: int) -> None:
         _check(lib().ccb_comm_set_max_ctas(self._h, ctas))
 
+    def set_noncooperative(self, ctas: int) -> None:
+        """Grids of at most `ctas` CTAs are launched plainly instead of cooperatively (0 = never):
+        for collectives overlapped with compute on another stream, with set_max_ctas()."""
+        L = lib()
+        L.ccb_comm_set_noncooperative.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        _check(L.ccb_comm_set_noncooperative(self._h, ctas))
+
     def set_waves(self, waves: int) -> None:
         L = lib()
         L.ccb_comm_set_waves.argtypes = [ctypes.c_void_p, ctypes.c_int]
         _check(L.ccb_comm_set_waves(self._h, waves))
 
-    def set_pipeline(self, mode: int = 1, link_warps: int = 0, multicast: bool = True) -> None:
+    def set_pipeline(self, mode: int = 1, link_warps: int = 0, multicast: bool = False) -> None:
         """The warp-specialised pipelined two-shot kernel: mode 0 never, 1 when the message is
         large enough, 2 always; link_warps of a CTA's 31 data warps store over NVLink (0 keeps
         the current value); multicast lets phase 2 store once through an NVLS mapping."""

@@ -143,10 +143,11 @@ struct ccb_comm {
   int num_sms = 0;
   int max_ctas = 0;
   int waves = 0;  // 0 = choose per call
+  int noncoop_ctas = 0;     // grids of at most this many CTAs are launched without the cooperative attribute
   int pipe_mode = 1;        // 0 = never use the pipelined two-shot kernel, 1 = when large enough, 2 = always
   int pipe_min_chunks = 4;  // chunks (4096 elements) per CTA from which it is used
-  int pipe_link_warps = 24; // of the 31 data warps of a CTA, how many store over NVLink
-  int pipe_mc = 1;          // phase 2 through the NVLS multicast mapping when there is one
+  int pipe_link_warps = 20; // of the 31 data warps of a CTA, how many store over NVLink
+  int pipe_mc = 0;          // phase 2 through the NVLS multicast mapping (measured slower at 2 and 4 GPUs: off)
   unsigned long long* trace = nullptr;  // device buffer, CCB_MAX_CTAS * nlocal * CCB_TRACE_SLOTS
   bool dead = false;
   // ownership
@@ -177,12 +178,13 @@ static int finish_common(ccb_comm* c) {
   c->timeout_ns = env_u64("CCB_TIMEOUT_MS", 10000) * 1000000ull;
   c->max_ctas = (int)env_u64("CCB_MAX_CTAS", 0);
   c->waves = (int)env_u64("CCB_WAVES", 0);
+  c->noncoop_ctas = (int)env_u64("CCB_NONCOOP_CTAS", 0);
   c->pipe_mode = (int)env_u64("CCB_PIPE", 1);
   c->pipe_min_chunks = (int)env_u64("CCB_PIPE_MIN_CHUNKS", 4);
-  c->pipe_link_warps = (int)env_u64("CCB_PIPE_LINK_WARPS", 24);
+  c->pipe_link_warps = (int)env_u64("CCB_PIPE_LINK_WARPS", 20);
   if (c->pipe_link_warps < 1) c->pipe_link_warps = 1;
   if (c->pipe_link_warps > 30) c->pipe_link_warps = 30;
-  c->pipe_mc = (int)env_u64("CCB_PIPE_MC", 1);
+  c->pipe_mc = (int)env_u64("CCB_PIPE_MC", 0);
   RT_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), CCB_STATUS_WORDS * 4, cudaHostAllocMapped));
   memset(c->status_host, 0, CCB_STATUS_WORDS * 4);
   RT_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
@@ -228,7 +230,15 @@ int grid_cap(ccb_comm* c, const void* kernel, int threads) {
 int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream, int threads) {
   dim3 grid((unsigned)ctas, (unsigned)c->nlocal, 1), block((unsigned)threads, 1, 1);
   void* params[] = {args};
-  cudaError_t e = cudaLaunchCooperativeKernel(kernel, grid, block, params, 0, stream);
+  // A cooperative launch starts only when the WHOLE grid fits beside what is running, so
+  // behind a stream of GEMMs it waits for a full wave to drain. With one rank per launch
+  // no CTA waits on another CTA of its own grid (only on the same-numbered CTA of the
+  // peers, whose GPUs make progress independently), so a small grid may be launched
+  // plainly: its CTAs start one by one as SMs free up. Launches that play several ranks
+  // (CTAs of one grid wait on each other) always stay cooperative.
+  const bool plain = c->nlocal == 1 && c->noncoop_ctas > 0 && ctas <= c->noncoop_ctas;
+  cudaError_t e = plain ? cudaLaunchKernel(kernel, grid, block, params, 0, stream)
+                        : cudaLaunchCooperativeKernel(kernel, grid, block, params, 0, stream);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
     return CCB_ERR_CUDA;
@@ -562,6 +572,11 @@ extern "C" int ccb_comm_set_timeout_ms(ccb_comm* c, uint64_t ms) {
 extern "C" int ccb_comm_set_max_ctas(ccb_comm* c, int ctas) {
   if (!c) return CCB_ERR_ARG;
   c->max_ctas = ctas;
+  return CCB_OK;
+}
+extern "C" int ccb_comm_set_noncooperative(ccb_comm* c, int ctas) {
+  if (!c || ctas < 0) return CCB_ERR_ARG;
+  c->noncoop_ctas = ctas;
   return CCB_OK;
 }
 extern "C" int ccb_comm_set_trace(ccb_comm* c, int on) {

@@ -50,13 +50,20 @@ uint64_t ccb_comm_arena_bytes(const ccb_comm* c);
 int ccb_comm_set_timeout_ms(ccb_comm* c, uint64_t ms);
 /* Cap on CTAs per rank (0 = as many as fit). */
 int ccb_comm_set_max_ctas(ccb_comm* c, int ctas);
+/* Grids of at most `ctas` CTAs per rank are launched without the cooperative attribute
+ * (0 = always cooperative, the default; also CCB_NONCOOP_CTAS). Use it together with
+ * ccb_comm_set_max_ctas() for collectives that should hide behind compute on another
+ * stream: a plain launch trickles into SMs as they free up instead of waiting for room
+ * for the whole grid. One rank per process only; every wait stays bounded. */
+int ccb_comm_set_noncooperative(ccb_comm* c, int ctas);
 /* Software-pipeline depth of the two-shot kernels (0 = choose per call, at most 8). */
 int ccb_comm_set_waves(ccb_comm* c, int waves);
 /* The warp-specialised pipelined two-shot kernel (large AllReduce / ReduceScatter):
  * mode 0 = never, 1 = when the message is large enough (default), 2 = always;
  * link_warps = how many of a CTA's 31 data warps store over NVLink (1 to 30; 0 keeps the
- * current value, default 24; the rest decode); mc != 0 lets its second phase store once to the
- * NVLS multicast address when the communicator has one. Also CCB_PIPE,
+ * current value, default 20; the rest decode); mc != 0 lets its second phase store once to the
+ * NVLS multicast address when the communicator has one (off by default: measured slower than
+ * per-peer stores at 2 and 4 GPUs). Also CCB_PIPE,
  * CCB_PIPE_LINK_WARPS, CCB_PIPE_MC, CCB_PIPE_MIN_CHUNKS in the environment. */
 int ccb_comm_set_pipeline(ccb_comm* c, int mode, int link_warps, int mc);
 /* Copies the CCB_STATUS_WORDS status words; returns CCB_ERR_TIMEOUT when a kernel of

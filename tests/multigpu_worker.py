@@ -116,7 +116,67 @@ def _body(comm, rank, world, dev):
         ex = sum(t.double() for t in xs).float()
         assert torch.allclose(red.cpu(), ex, rtol=1e-5, atol=1e-5)
     assert comm.status()[0] == 0
+    _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs)
     _sz_and_moe(comm, rank, world, dev, gather_inputs)
+
+
+def _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs):
+    """The pipelined two-shot kernel over real peers (with and without the multicast second
+    phase), and small grids launched without the cooperative attribute."""
+    count = (1 << 23) + 4097
+    g = torch.Generator(device=dev).manual_seed(77 + rank)
+    x = (torch.randn(count, generator=g, device=dev) * (rank + 1)).to(torch.bfloat16)
+    xs = gather_inputs(x)
+    exact = sum(t.double() for t in xs).float()
+    results = {}
+    for name, mode, mc in (("plain", 0, False), ("pipe", 2, False), ("pipe_mc", 2, True)):
+        if mc and not comm.has_nvls:
+            continue
+        comm.set_pipeline(mode, multicast=mc)
+        comm.set_waves(4 if mode else 0)
+        y = torch.empty_like(x)
+        for _ in range(3):
+            comm.all_reduce(x, y, codec="int8", algo="twoshot")
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0, (name, comm.status())
+        results[name] = y.float().cpu()
+        rel = ((results[name] - exact).norm() / exact.norm()).item()
+        assert rel < 0.03, (name, rel)
+        ys = gather_inputs(y)
+        assert all(torch.equal(ys[0], t) for t in ys), name
+    scale = results["plain"].abs().max().item()
+    for name in results:
+        d = (results[name] - results["plain"]).abs()
+        assert (d > 1e-5 * scale).float().mean().item() < 2e-3, name
+    # reduce_scatter through the pipelined kernel
+    per = 1 << 21
+    xr = torch.randn(per * world, device=dev) * (rank + 1)
+    xrs = gather_inputs(xr)
+    out = torch.empty(per, device=dev)
+    comm.set_pipeline(2)
+    comm.set_waves(4)
+    comm.reduce_scatter(xr, out, codec="int8")
+    torch.cuda.synchronize()
+    ex = sum(t[rank * per:(rank + 1) * per].double() for t in xrs).float()
+    assert ((out.cpu() - ex).norm() / ex.norm()).item() < 0.03
+    comm.set_pipeline(1)
+    comm.set_waves(0)
+    # few CTAs, plain (non-cooperative) launches: what the overlap benchmark uses
+    comm.set_max_ctas(8)
+    comm.set_noncooperative(8)
+    for algo in ("twoshot", "ring"):
+        y = torch.empty_like(x)
+        for _ in range(3):
+            comm.all_reduce(x, y, codec="int8", algo=algo)
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0
+        assert ((y.float().cpu() - exact).norm() / exact.norm()).item() < 0.06, algo
+    comm.reduce_scatter(xr, out, codec="int8")
+    torch.cuda.synchronize()
+    assert ((out.cpu() - ex).norm() / ex.norm()).item() < 0.03
+    comm.set_max_ctas(0)
+    comm.set_noncooperative(0)
+    assert comm.status()[0] == 0
 
 
 def _sz_and_moe(comm, rank, world, dev, gather_inputs):

@@ -136,5 +136,6 @@ def test_all_chunks_of_a_hook_call_are_one_launch():
     assert launch_count() - n0 == 3
     torch.cuda.synchronize()
     want = torch.cat([C.roundtrip(x.cpu()[c * per:(c + 1) * per], "int8") for c in range(chunks)])
-    assert torch.equal(out.cpu().float(), want.float())
-    assert torch.equal(acc.cpu(), (want.float() + 1).to(torch.bfloat16))
+    assert torch.equal(out.cpu(), want.float().to(torch.bfloat16))
+    # decode and add contract into one fused multiply-add: equal up to one rounding of the 16-bit result
+    assert (acc.cpu().float() - (want.float() + 1)).abs().max().item() <= 2.0 ** -7 * (want.abs().max().item() + 1)

@@ -108,7 +108,7 @@ def test_role_splits(comms, link_warps):
     comm.set_waves(3)
     comm.set_pipeline(2, link_warps=link_warps)
     piped = run()
-    comm.set_pipeline(1, link_warps=24)
+    comm.set_pipeline(1, link_warps=20)
     comm.set_waves(0)
     assert comm.status()[0] == 0
     for r in range(n):
