@@ -14,7 +14,7 @@ import subprocess
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
-BIN = ROOT / "bin"
+BIN = Path(os.environ["CCB_BIN_DIR"]) if os.environ.get("CCB_BIN_DIR") else ROOT / "bin"   # build outputs (default: in-tree)
 CUDA = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 INC = [ROOT / "include" / "ccb" / "compat", ROOT / "include", ROOT / "userconfig" / "deviation_metric_examples",
        CUDA / "include"]

@@ -14,7 +14,9 @@ def build(verbose: bool = False) -> None:
     root, libs = nb.ROOT, nb.BIN / "libs"
     real = nb.have_mpi()
     cc = "mpicc" if real else "gcc"
-    inc, link = [], ["-lm", "-ldl", "-lpthread"]
+    # with an installed MPI the compiler wrapper brings the include and link flags, and
+    # HAVE_MPI tells user code so (the reference's build_tests.sh:118-121 does the same)
+    inc, link = (["-DHAVE_MPI"] if real else []), ["-lm", "-ldl", "-lpthread"]
     if not real:
         mini = nb.cc(libs / "libccb_minimpi.so", [root / "csrc/minimpi/minimpi.c"], shared=True, verbose=verbose)
         inc = [f"-I{root / 'csrc/minimpi'}"]

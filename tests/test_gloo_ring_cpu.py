@@ -19,7 +19,9 @@ def _worker(rank, world, port, count, codec, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     x = torch.randn(count, generator=torch.Generator().manual_seed(100 + rank)) * (rank + 1)
     y = ring_all_reduce(x, codec)
-    q.put((rank, y))
+    # plain bytes, not a tensor: a tensor travels through a shared-memory handshake with this
+    # process, which may already have exited when the parent asks for it
+    q.put((rank, y.numpy().tobytes()))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -34,7 +36,9 @@ def test_ring_matches_the_restatement(world, count, codec):
     procs = [ctx.Process(target=_worker, args=(r, world, port, count, codec, q)) for r in range(world)]
     for p in procs:
         p.start()
-    got = dict(q.get(timeout=300) for _ in range(world))
+    import numpy as np
+
+    got = {r: torch.from_numpy(np.frombuffer(b, dtype=np.float32).copy()) for r, b in (q.get(timeout=300) for _ in range(world))}
     for p in procs:
         p.join(timeout=60)
     xs = [torch.randn(count, generator=torch.Generator().manual_seed(100 + r)) * (r + 1) for r in range(world)]

@@ -35,3 +35,23 @@ def test_clock_summary_reads_nvidia_smi_rows(tmp_path):
     out = s.summary()
     assert out["sm_mhz"] == 1950 and out["sm_max_mhz"] == 1965 and out["reasons"] == ["sw_power_cap"] and out["samples"] == 3
     assert s.gpu_index == "0,1"
+
+
+def test_environment_probe_reports_the_reference_schema():
+    """Top-level keys of the reference's probe plus what this framework adds; runs anywhere."""
+    import json
+
+    from ccbench_b200.utils import detect_env
+
+    info = detect_env.detect()
+    json.dumps(info)   # serialisable
+    for key in ("timestamp", "hostname", "ccbench_dir", "cpu", "memory", "gpu", "cuda", "nccl", "mpi", "ib", "network", "ucx", "slurm",
+                "slurm_allocation", "compiler", "python", "os", "modules_loaded", "plugin_projects", "disk", "datasets", "environment",
+                "current_config", "built"):
+        assert key in info, key
+    assert info["cpu"]["cores"] >= 1 and info["memory"]["total_gb"] > 0
+    assert set(info["gpu"]) >= {"nvidia_present", "nvidia_count", "nvidia_devices", "amd_present", "amd_count"}
+    assert set(info["cuda"]) >= {"found", "version", "nvcc_path", "cuda_home"}
+    assert set(info["mpi"]) >= {"found", "implementation", "version", "compiler"}
+    assert info["current_config"].get("communication_arch") in ("nccl", "mpi", "rccl")
+    assert isinstance(info["network"]["interfaces"], list) and info["compiler"]["gcc"]
