@@ -155,7 +155,35 @@ def main(argv=None):
                 codec, algo = parts[0], parts[1] if len(parts) > 1 else "auto"
                 comm.set_waves(int(parts[2]) if len(parts) > 2 else 0)
                 comm.set_max_ctas(int(parts[3]) if len(parts) > 3 else 0)
-                if algo == "nvls" and not comm.has_nvls:
+                if algo in ("nvls", "nvls_inplace") and not comm.has_nvls:
+                    continue
+                if algo == "nvls_inplace":
+                    # symmetric (arena-backed) tensor, reduced in place through the switch; the
+                    # values grow from call to call, which does not change the time
+                    if count * es > comm.arena_bytes // 2:
+                        continue
+                    xs = comm.symmetric_empty(count, dtype)
+                    xs.copy_(x)
+
+                    def fn():
+                        comm.all_reduce(xs, codec="none", algo="nvls")
+
+                    t = timed(fn, args.iters, args.warmup, world, dev, flush if size < args.flush_below else None)
+                    xs.copy_(x)
+                    fn()
+                    y.copy_(xs)
+                    del xs
+                    comm.symmetric_free_all()
+                    if comm.status()[0] != 0:
+                        raise SystemExit(f"communicator failed: {comm.status()}")
+                    rel = ((y.float() - exact).norm() / (exact.norm() + 1e-30)).item()
+                    bytes_ = count * es
+                    algbw = bytes_ / (t * 1e-6) / 1e9
+                    bus = algbw * (2 * (world - 1) / world if world > 1 else 1.0)
+                    row = f"{bytes_},{world},{args.dtype},nvls_inplace,none,{t:.2f},{algbw:.2f},{bus:.2f},{2 * algbw:.2f},1.000,{rel:.3e}"
+                    rows.append(row)
+                    if rank == 0:
+                        print(row, flush=True)
                     continue
 
                 def fn():

@@ -137,6 +137,38 @@ class Communicator:
         _check(L.ccb_comm_read_trace(self._h, out.data_ptr(), ctas))
         return out
 
+    # ------------------------------------------------- symmetric allocations --
+    def symmetric_empty(self, numel: int, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """A tensor INSIDE the symmetric arena (same offset on every rank when all ranks make
+        the same sequence of calls). all_reduce(..., algo="nvls") on such tensors runs in place
+        through the NVSwitch, without staging copies. The tensor must not outlive the communicator."""
+        L = lib()
+        L.ccb_comm_symm_alloc.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64)]
+        L.ccb_comm_symm_ptr.argtypes = [ctypes.c_void_p, ctypes.c_uint64]
+        L.ccb_comm_symm_ptr.restype = ctypes.c_void_p
+        nbytes = numel * torch.empty((), dtype=dtype).element_size()
+        off = ctypes.c_uint64(0)
+        _check(L.ccb_comm_symm_alloc(self._h, max(nbytes, 16), ctypes.byref(off)))
+        ptr = L.ccb_comm_symm_ptr(self._h, off.value)
+
+        class _Span:   # what torch needs to wrap foreign device memory
+            __cuda_array_interface__ = {"shape": (max(nbytes, 16),), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+        t = torch.as_tensor(_Span(), device=self.device)[:nbytes].view(dtype)
+        if not hasattr(self, "_symm"):
+            self._symm = {}
+        self._symm[t.data_ptr()] = (off.value, nbytes)
+        return t
+
+    def symmetric_free_all(self) -> None:
+        lib().ccb_comm_symm_free_all.argtypes = [ctypes.c_void_p]
+        _check(lib().ccb_comm_symm_free_all(self._h))
+        self._symm = {}
+
+    def _symm_offset(self, t: torch.Tensor):
+        hit = getattr(self, "_symm", {}).get(t.data_ptr())
+        return hit[0] if hit and t.numel() * t.element_size() <= hit[1] else None
+
     def status(self) -> tuple[int, list[int]]:
         words = (ctypes.c_uint32 * 8)()
         rc = lib().ccb_comm_status(self._h, words)
@@ -177,6 +209,14 @@ class Communicator:
         ep, et = self._ptrs(error_feedback, "error_feedback")
         if et is not None and any(e.dtype != torch.float32 or e.numel() != st[0].numel() for e in et):
             raise ValueError("error_feedback must be float32 with send's element count")
+        if algo == "nvls" and self.nlocal == 1 and op == "sum" and error_feedback is None:
+            so, ro = self._symm_offset(st[0]), self._symm_offset(rt[0])
+            if so is not None and ro is not None:   # both live in the arena: in place through the switch
+                L = lib()
+                L.ccb_all_reduce_symm.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int,
+                                                  ctypes.c_void_p]
+                _check(L.ccb_all_reduce_symm(self._h, so, ro, st[0].numel(), self._dtype(st), self._stream()))
+                return recv
         if algo == "auto":   # a measured choice for this shape, when tune_all_reduce() made one
             algo = getattr(self, "_tuned", {}).get((st[0].numel(), st[0].dtype, codec), "auto")
         _check(lib().ccb_all_reduce(self._h, sp, rp, st[0].numel(), self._dtype(st), _code(op, K.OPS),

@@ -23,6 +23,9 @@ def build(verbose: bool = False) -> None:
         # lossless float codec behind the same four hooks (the reference's DietGPU wrapper role)
         ("libdietgpu_wrapper.so", root / "userconfig/wrapper_code_examples/compression/dietgpu/dietgpu.c",
          [str(dst), *nb.cuda_libs(), *rpath]),
+        # error-bounded GPU codec behind the four hooks (the reference's cuZFP wrapper role)
+        ("libzfp_for_gpu_nvidia.so", root / "userconfig/wrapper_code_examples/compression/zfp_for_gpu_nvidia/zfp_for_gpu_nvidia.c",
+         [str(dst), *nb.cuda_libs(), "-lm", *rpath]),
     ]:
         if src.exists():
             nb.cc(libs / name, [src], shared=True, libs=extra, verbose=verbose)

@@ -137,4 +137,44 @@ __global__ void __launch_bounds__(kThreads, 2) nvls_allreduce_kernel(const __gri
   }
 }
 
+// The same reduction IN PLACE on buffers that live inside the symmetric arena (allocated
+// with ccb_comm_symm_alloc at the same offset on every rank): no staging copy in, no copy
+// out. Each rank pulls the switch-reduced values of its own 1/n of the vectors straight
+// from everybody's input (multimem.ld_reduce) and pushes them into everybody's output
+// (multimem.st). Two all-rank flag rounds bracket it: inputs complete before anyone
+// reads, outputs complete before anyone returns. send_off == recv_off is allowed: the
+// vectors a rank reads and writes belong to no other rank's share.
+template <class T>
+__global__ void __launch_bounds__(kThreads, 2) nvls_inplace_kernel(const __grid_constant__ ReduceArgs a) {
+  __shared__ CtaSync sync;
+  const CommDev& c = a.c;
+  const int r = a.rank0, n = c.nranks;
+  const int b = blockIdx.x, G = gridDim.x;
+  char* my = c.arena[r];
+  const size_t send_off = (size_t)a.shard_elems, recv_off = (size_t)a.shard_pad;  // byte offsets inside the arena
+  const size_t vecs = (a.count * sizeof(T) + 15) / 16;                            // the host pads allocations to 16 bytes
+  const size_t per = (vecs + n - 1) / n, lo = (size_t)r * per, hi = lo + per < vecs ? lo + per : vecs;
+  if (threadIdx.x == 0) sync.fail = 0;
+  __syncthreads();
+  const uint32_t peers = ((1u << n) - 1u) & ~(1u << r);
+  // round 1: what earlier kernels of this stream wrote into the input is visible everywhere
+  if (threadIdx.x == 0) signal_peers(c, peers, 0, r, b);
+  if (!cta_wait_sources(sync, c, my, 0, r, 0xffu, 0x88)) return;
+  const char* mc_in = c.mc_arena + send_off;
+  char* mc_out = c.mc_arena + recv_off;
+  constexpr size_t kTileVecs = kThreads * 4;
+  for (size_t t0 = lo + (size_t)b * kTileVecs; t0 < hi; t0 += (size_t)G * kTileVecs) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const size_t vi = t0 + (size_t)u * kThreads + threadIdx.x;
+      if (vi >= hi) continue;
+      const uint4 x = Multimem<T>::ld_reduce(mc_in + vi * 16);
+      multimem_st(mc_out + vi * 16, x);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) signal_peers(c, peers, 1, r, b);
+  if (!cta_wait_sources(sync, c, my, 1, r, 0xffu, 0x98)) return;
+}
+
 }  // namespace ccb

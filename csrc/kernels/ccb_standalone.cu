@@ -65,6 +65,25 @@ __global__ void __launch_bounds__(kSaThreads) decode_kernel(const char* wire, si
   }
 }
 
+// inout += src, element-wise in T (one rounding): the "reduce" of hook libraries whose codec
+// decodes into a temporary (coccl_wrapper_template.cu:258-272 add_*_kernel in the reference).
+template <class T>
+__global__ void __launch_bounds__(kSaThreads) accumulate_kernel(const T* __restrict__ src, T* inout, size_t count) {
+  const size_t units = (count + kWarpElems - 1) / kWarpElems;
+  const size_t warp = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = ((size_t)gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (size_t u = warp; u < units; u += nwarps) {
+    const size_t idx = u * kWarpElems + (size_t)lane * kLaneElems;
+    if (idx >= count) continue;
+    float a[16], b[16];
+    load16<T>(src, idx, count, a);
+    load16<T>(inout, idx, count, b);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) b[i] += a[i];
+    store16<T>(inout, idx, count, b);
+  }
+}
+
 struct WireList {
   const char* w[16];
   int n;
@@ -260,6 +279,17 @@ extern "C" int ccb_decode_chunks(int codec, int dtype, const void* wire, uint64_
          : dtype == CCB_F16  ? decode_t<__half, 0>(codec, wire, chunk_count, out, pad, s, nchunks, wire_stride, chunk_count)
                              : CCB_ERR_UNSUPPORTED;
   return rc ? rc : finish("ccb_decode_chunks");
+}
+
+extern "C" int ccb_accumulate(int dtype, const void* src, void* inout, uint64_t count, void* stream) {
+  if (!count) return CCB_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int g = sa_grid((count + kWarpElems - 1) / kWarpElems);
+  if (dtype == CCB_F32) accumulate_kernel<float><<<g, kSaThreads, 0, s>>>((const float*)src, (float*)inout, count);
+  else if (dtype == CCB_BF16) accumulate_kernel<__nv_bfloat16><<<g, kSaThreads, 0, s>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)inout, count);
+  else if (dtype == CCB_F16) accumulate_kernel<__half><<<g, kSaThreads, 0, s>>>((const __half*)src, (__half*)inout, count);
+  else return CCB_ERR_UNSUPPORTED;
+  return finish("ccb_accumulate");
 }
 
 extern "C" int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out, void* stream) {

@@ -20,6 +20,7 @@
 
 #include "../kernels/ccb_exchange.cuh"
 #include "../kernels/ccb_nvls.cuh"
+#include "../kernels/ccb_p2p.cuh"
 #include "../kernels/ccb_reduce.cuh"
 #include "../kernels/ccb_ring.cuh"
 #include "ccb/ccb.h"
@@ -134,6 +135,11 @@ struct ccb_comm {
   int rank0 = 0, nlocal = 1, nranks = 1, device = 0;
   size_t arena_bytes = 0;   // per rank, mapped size
   size_t half_bytes = 0;
+  size_t symm_top = 0;      // symmetric allocations grow down from here
+  size_t symm_limit = 0;    // top of the allocatable part (below the point-to-point mailboxes)
+  size_t p2p_offset = 0;    // mailboxes of ccb_p2p: [source][lane][half][p2p_lane_bytes]; 0 = none
+  unsigned int p2p_lane_bytes = 0;
+  unsigned int p2p_sent[CCB_MAX_RANKS] = {}, p2p_rcvd[CCB_MAX_RANKS] = {};  // rounds exchanged so far, per peer and direction
   char* arena[CCB_MAX_RANKS] = {};
   char* mc_arena = nullptr;
   uint32_t* status_host = nullptr;
@@ -188,7 +194,23 @@ static int finish_common(ccb_comm* c) {
   RT_TRY(cudaHostAlloc(reinterpret_cast<void**>(&c->status_host), CCB_STATUS_WORDS * 4, cudaHostAllocMapped));
   memset(c->status_host, 0, CCB_STATUS_WORDS * 4);
   RT_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&c->status_dev), c->status_host, 0));
-  c->half_bytes = ((c->arena_bytes - CCB_DATA_OFFSET) / 2) & ~(size_t)255;
+  // Point-to-point mailboxes at the top of the arena (1/64 of it per source, at most 8 MiB):
+  // two halves per (source, lane). Communicators with one rank, or playing several ranks
+  // in one process, have none.
+  c->symm_limit = c->arena_bytes;
+  if (c->nranks > 1 && c->nlocal == 1) {
+    size_t lane = c->arena_bytes / 64 / (2 * kP2pLanes);
+    if (lane > (256u << 10)) lane = 256u << 10;
+    lane &= ~(size_t)255;
+    const size_t total = (size_t)CCB_MAX_RANKS * kP2pLanes * 2 * lane;
+    if (lane >= 4096 && total + CCB_DATA_OFFSET < c->arena_bytes / 2) {
+      c->p2p_lane_bytes = (unsigned int)lane;
+      c->p2p_offset = (c->arena_bytes - total) & ~(size_t)4095;
+      c->symm_limit = c->p2p_offset;
+    }
+  }
+  c->symm_top = c->symm_limit;
+  c->half_bytes = ((c->symm_top - CCB_DATA_OFFSET) / 2) & ~(size_t)255;
   return CCB_OK;
 }
 
@@ -573,6 +595,140 @@ extern "C" int ccb_comm_set_max_ctas(ccb_comm* c, int ctas) {
   if (!c) return CCB_ERR_ARG;
   c->max_ctas = ctas;
   return CCB_OK;
+}
+// ---- symmetric allocations: user buffers inside the arena, same offset on every rank ----
+extern "C" int ccb_comm_symm_alloc(ccb_comm* c, uint64_t bytes, uint64_t* offset) {
+  if (!c || !offset || bytes == 0) return CCB_ERR_ARG;
+  const size_t need = round_up(bytes, 4096);
+  // staging keeps at least a quarter of the arena
+  if (need > c->symm_top || c->symm_top - need < CCB_DATA_OFFSET + c->arena_bytes / 4) {
+    set_error("symmetric allocation of %llu bytes does not fit (arena %llu bytes, %llu already taken)", (unsigned long long)bytes,
+              (unsigned long long)c->arena_bytes, (unsigned long long)(c->symm_limit - c->symm_top));
+    return CCB_ERR_CAPACITY;
+  }
+  RT_TRY(cudaDeviceSynchronize());  // no call may be using the staging that shrinks
+  c->symm_top -= need;
+  c->half_bytes = ((c->symm_top - CCB_DATA_OFFSET) / 2) & ~(size_t)255;
+  *offset = c->symm_top;
+  return CCB_OK;
+}
+extern "C" void* ccb_comm_symm_ptr(ccb_comm* c, uint64_t offset) {
+  if (!c || offset < c->symm_top || offset >= c->symm_limit) return nullptr;
+  return c->arena[c->rank0] + offset;
+}
+extern "C" int ccb_comm_symm_free_all(ccb_comm* c) {
+  if (!c) return CCB_ERR_ARG;
+  RT_TRY(cudaDeviceSynchronize());
+  // Point-to-point mailboxes at the top of the arena (1/64 of it per source, at most 8 MiB):
+  // two halves per (source, lane). Communicators with one rank, or playing several ranks
+  // in one process, have none.
+  c->symm_limit = c->arena_bytes;
+  if (c->nranks > 1 && c->nlocal == 1) {
+    size_t lane = c->arena_bytes / 64 / (2 * kP2pLanes);
+    if (lane > (256u << 10)) lane = 256u << 10;
+    lane &= ~(size_t)255;
+    const size_t total = (size_t)CCB_MAX_RANKS * kP2pLanes * 2 * lane;
+    if (lane >= 4096 && total + CCB_DATA_OFFSET < c->arena_bytes / 2) {
+      c->p2p_lane_bytes = (unsigned int)lane;
+      c->p2p_offset = (c->arena_bytes - total) & ~(size_t)4095;
+      c->symm_limit = c->p2p_offset;
+    }
+  }
+  c->symm_top = c->symm_limit;
+  c->half_bytes = ((c->symm_top - CCB_DATA_OFFSET) / 2) & ~(size_t)255;
+  return CCB_OK;
+}
+extern "C" int ccb_all_reduce_symm(ccb_comm* c, uint64_t send_off, uint64_t recv_off, uint64_t count, int dtype, ccb_stream_t stream_) {
+  int rc = check_alive(c);
+  if (rc) return rc;
+  if (!c->mc_arena || c->nlocal != 1) {
+    set_error("in-place NVLS all-reduce needs a communicator with a multicast mapping and one rank per process");
+    return CCB_ERR_UNSUPPORTED;
+  }
+  const size_t bytes = round_up(count * elem_size(dtype), 16);
+  if (count == 0) return CCB_OK;
+  if (send_off < c->symm_top || recv_off < c->symm_top || send_off + bytes > c->symm_limit || recv_off + bytes > c->symm_limit ||
+      (send_off & 15) || (recv_off & 15)) {
+    set_error("buffers of an in-place all-reduce must come from ccb_comm_symm_alloc");
+    return CCB_ERR_ARG;
+  }
+  const void* fn = dtype == CCB_F32    ? reinterpret_cast<const void*>(&nvls_inplace_kernel<float>)
+                   : dtype == CCB_BF16 ? reinterpret_cast<const void*>(&nvls_inplace_kernel<__nv_bfloat16>)
+                   : dtype == CCB_F16  ? reinterpret_cast<const void*>(&nvls_inplace_kernel<__half>)
+                                       : nullptr;
+  if (!fn) return CCB_ERR_UNSUPPORTED;
+  ReduceArgs a;
+  memset(&a, 0, sizeof(a));
+  a.c = comm_dev(c, next_epoch(c));
+  a.count = count;
+  a.shard_elems = send_off;  // the in-place kernel reads these two fields as arena byte offsets
+  a.shard_pad = recv_off;
+  a.rank0 = c->rank0;
+  a.nlocal = 1;
+  const size_t vecs = bytes / 16, per = (vecs + c->nranks - 1) / c->nranks;
+  const size_t tiles = (per + kThreads * 4 - 1) / (kThreads * 4);
+  const int cap = grid_cap(c, fn);
+  return launch(c, fn, tiles < (size_t)cap ? (int)(tiles ? tiles : 1) : cap, &a, static_cast<cudaStream_t>(stream_));
+}
+// ---- point-to-point over the peer arenas --------------------------------------------------
+// ops: `nops` sends and receives of THIS rank, all launched as one kernel (what an
+// ncclGroupStart/End holds, or one call). Message sizes must match at the two ends.
+extern "C" int ccb_p2p(ccb_comm* c, const ccb_p2p_op* ops, int nops, ccb_stream_t stream_) {
+  int rc = check_alive(c);
+  if (rc) return rc;
+  if (!ops || nops < 1 || nops > kP2pMaxOps) {
+    set_error("ccb_p2p takes 1 to %d operations per call", kP2pMaxOps);
+    return CCB_ERR_ARG;
+  }
+  if (!c->p2p_offset) {
+    set_error("this communicator has no point-to-point mailboxes (one rank per process and an arena of at least 64 MiB are needed)");
+    return CCB_ERR_UNSUPPORTED;
+  }
+  P2pArgs a;
+  memset(&a, 0, sizeof(a));
+  a.c = comm_dev(c, c->epoch ? c->epoch : 1);   // point-to-point does not advance the collectives' epoch
+  a.box_offset = c->p2p_offset;
+  a.lane_bytes = c->p2p_lane_bytes;
+  a.rank = c->rank0;
+  const size_t round_bytes = (size_t)kP2pLanes * c->p2p_lane_bytes;
+  int k = 0;
+  for (int i = 0; i < nops; ++i) {
+    const ccb_p2p_op& o = ops[i];
+    if (o.peer < 0 || o.peer >= c->nranks || o.peer == c->rank0 || (!o.buf && o.bytes)) {
+      set_error("ccb_p2p: bad peer %d or null buffer", o.peer);
+      return CCB_ERR_ARG;
+    }
+    if (o.bytes == 0) continue;
+    unsigned int* ctr = o.is_recv ? &c->p2p_rcvd[o.peer] : &c->p2p_sent[o.peer];
+    a.op[k].buf = o.buf;
+    a.op[k].bytes = o.bytes;
+    a.op[k].peer = o.peer;
+    a.op[k].is_recv = o.is_recv ? 1 : 0;
+    a.op[k].first_round = *ctr;
+    *ctr += (unsigned int)((o.bytes + round_bytes - 1) / round_bytes);
+    ++k;
+  }
+  if (k == 0) return CCB_OK;
+  a.nops = k;
+  dim3 grid(kP2pLanes, (unsigned)k, 1), block(kThreads, 1, 1);
+  void* params[] = {&a};
+  // the lanes of one operation do not wait on each other, and the two ends of a transfer
+  // run on different GPUs: a plain launch is enough
+  cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(&p2p_kernel), grid, block, params, 0, static_cast<cudaStream_t>(stream_));
+  if (e != cudaSuccess) {
+    set_error("p2p launch failed: %s", cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  count_launch();
+  return CCB_OK;
+}
+extern "C" int ccb_send(ccb_comm* c, const void* buf, uint64_t bytes, int peer, ccb_stream_t stream) {
+  ccb_p2p_op o = {const_cast<void*>(buf), bytes, peer, 0};
+  return ccb_p2p(c, &o, 1, stream);
+}
+extern "C" int ccb_recv(ccb_comm* c, void* buf, uint64_t bytes, int peer, ccb_stream_t stream) {
+  ccb_p2p_op o = {buf, bytes, peer, 1};
+  return ccb_p2p(c, &o, 1, stream);
 }
 extern "C" int ccb_comm_set_noncooperative(ccb_comm* c, int ctas) {
   if (!c || ctas < 0) return CCB_ERR_ARG;

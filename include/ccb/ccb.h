@@ -78,6 +78,37 @@ int ccb_comm_read_trace(ccb_comm* c, unsigned long long* out, int ctas);
 /* Wire bytes a call moves per rank for `count` elements (for ratio reporting). */
 uint64_t ccb_wire_bytes(int codec, int dtype, uint64_t count);
 
+/* ---- point-to-point ----------------------------------------------------------------
+ * Sends and receives over the peer arenas, no NCCL involved: the sender stores into a
+ * mailbox in the receiver's arena, the receiver copies out. ccb_p2p launches the
+ * operations of one rank (at most 16: the content of one ncclGroupStart/End) as ONE
+ * kernel, so a rank may send and receive at the same time. The byte counts of a send and
+ * of the matching receive must be equal; transfers between a pair are matched in issue
+ * order. A send of up to two rounds (2 x 16 x lane bytes, 8 MiB with the default arena)
+ * completes without its receive being posted, longer ones wait for it (bounded). */
+typedef struct ccb_p2p_op {
+  void* buf;
+  uint64_t bytes;
+  int peer;
+  int is_recv;
+} ccb_p2p_op;
+int ccb_p2p(ccb_comm* c, const ccb_p2p_op* ops, int nops, ccb_stream_t stream);
+int ccb_send(ccb_comm* c, const void* buf, uint64_t bytes, int peer, ccb_stream_t stream);
+int ccb_recv(ccb_comm* c, void* buf, uint64_t bytes, int peer, ccb_stream_t stream);
+
+/* ---- symmetric allocations -------------------------------------------------------
+ * User buffers INSIDE the arena, so that collectives can work on them in place. Every
+ * rank must make the same sequence of allocations (same sizes): buffers then sit at the
+ * same offset everywhere. Allocation synchronises the device and shrinks the staging the
+ * other collectives use; at most three quarters of the arena can be given out. */
+int ccb_comm_symm_alloc(ccb_comm* c, uint64_t bytes, uint64_t* offset);
+void* ccb_comm_symm_ptr(ccb_comm* c, uint64_t offset);   /* this rank's device address */
+int ccb_comm_symm_free_all(ccb_comm* c);
+/* Uncompressed sum of `count` elements, in place on symmetric buffers (send_off may equal
+ * recv_off), reduced inside the NVSwitch: needs a communicator created with the NVLS
+ * flag. No staging copies: the kernel only moves what must cross the links. */
+int ccb_all_reduce_symm(ccb_comm* c, uint64_t send_off, uint64_t recv_off, uint64_t count, int dtype, ccb_stream_t stream);
+
 /* Kernels launched by this library since it was loaded. */
 uint64_t ccb_launch_count(void);
 const char* ccb_last_error(void);
@@ -119,6 +150,8 @@ int ccb_encode_chunks(int codec, int dtype, const void* in, uint64_t chunk_count
                       uint64_t wire_stride, ccb_stream_t stream);
 int ccb_decode_chunks(int codec, int dtype, const void* wire, uint64_t wire_stride, uint64_t chunk_count, uint64_t nchunks,
                       void* out, int accumulate, ccb_stream_t stream);
+/* inout += src, element-wise in the element type. */
+int ccb_accumulate(int dtype, const void* src, void* inout, uint64_t count, ccb_stream_t stream);
 /* wire_out = encode(sum_k decode(wires[k])), 1 <= nwires <= 16 */
 int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out,
                       ccb_stream_t stream);

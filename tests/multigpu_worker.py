@@ -148,6 +148,29 @@ def _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs):
     for name in results:
         d = (results[name] - results["plain"]).abs()
         assert (d > 1e-5 * scale).float().mean().item() < 2e-3, name
+    # uncompressed sum in place on symmetric (arena-backed) tensors, reduced inside the switch
+    if comm.has_nvls:
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+            n_el = (1 << 20) + 8
+            src = (torch.randn(n_el, generator=g, device=dev) * (rank + 1)).to(dtype)
+            want = sum(t.double() for t in gather_inputs(src)).float()
+            a = comm.symmetric_empty(n_el, dtype)
+            b = comm.symmetric_empty(n_el, dtype)
+            a.copy_(src)
+            comm.all_reduce(a, b, codec="none", algo="nvls")      # out of place, both in the arena
+            torch.cuda.synchronize()
+            assert ((b.float().cpu() - want).norm() / want.norm()).item() < tol, ("symm", dtype)
+            assert torch.equal(a, src)
+            comm.all_reduce(a, codec="none", algo="nvls")         # in place
+            torch.cuda.synchronize()
+            assert comm.status()[0] == 0
+            assert ((a.float().cpu() - want).norm() / want.norm()).item() < tol, ("symm in place", dtype)
+            # ordinary collectives still work with the smaller staging
+            y2 = torch.empty_like(src)
+            comm.all_reduce(src, y2, codec="int8", algo="twoshot")
+            torch.cuda.synchronize()
+            assert ((y2.float().cpu() - want).norm() / want.norm()).item() < 0.03
+            comm.symmetric_free_all()
     # reduce_scatter through the pipelined kernel
     per = 1 << 21
     xr = torch.randn(per * world, device=dev) * (rank + 1)

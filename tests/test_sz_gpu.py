@@ -105,3 +105,67 @@ def test_container_roundtrip_and_file(tmp_path):
     bad[0] ^= 0xFF
     with pytest.raises(ValueError):
         sz.from_container(bad)
+
+
+def test_numpy_codec_reads_gpu_written_bytes_and_the_gpu_reads_numpy_written_bytes():
+    """The on-disk container pinned from both sides: what the GPU wrote is decoded by the NumPy
+    codec to the very values the GPU decoder produces, and a container written by the NumPy
+    encoder is decoded by the GPU kernel to the NumPy decoder's values."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(20, 19, 70, generator=g).cumsum(-1).mul_(0.05)   # ragged tiles on every axis
+    x[3, 4, 5] = 1e30                                                 # forces one raw tile
+    eb = 2e-3
+    xg = x.cuda()
+    buf, _ = sz.compress(xg, eb)
+    want = sz.decompress(buf, x.shape, eb).cpu().numpy()
+    blob = sz.to_container(buf, x.shape, eb).cpu().numpy()
+    assert np.array_equal(sz.decode_cpu(blob), want)
+    cpu_blob = sz.encode_cpu(x.numpy(), eb)
+    back, shape, eb2 = sz.from_container(torch.from_numpy(cpu_blob).cuda())
+    got = sz.decompress(back, shape, eb2).cpu().numpy()
+    assert np.array_equal(got, sz.decode_cpu(cpu_blob))
+    fin = np.isfinite(x.numpy()) & (np.abs(x.numpy()) < 1e20)
+    assert np.abs(got[fin] - x.numpy()[fin]).max() <= float(np.float32(eb))
+
+
+def test_error_bounded_hook_library():
+    """The error-bounded codec behind ncclCompress / ncclDecompress / ncclDecompressReduce /
+    ncclDecompReduceComp (the cuZFP wrapper's role): chunk header, bound, reduction."""
+    import ctypes
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parent.parent / "bin" / "libs" / "libzfp_for_gpu_nvidia.so"
+    assert path.exists(), f"{path} is not built (python -m ccbench_b200.cli build)"
+    import os
+
+    os.environ["ZFP_PRECISION"] = "10"   # absolute bound 2^-10
+    L = ctypes.CDLL(str(path))
+    vp, szt, i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+    L.ncclCompressedChunkBytes.argtypes, L.ncclCompressedChunkBytes.restype = [szt, i], szt
+    L.ncclCompress.argtypes = [vp, ctypes.POINTER(vp), szt, i, ctypes.POINTER(szt), ctypes.POINTER(i), szt, i, i, vp]
+    L.ncclDecompress.argtypes = [vp, vp, szt, i, szt, i, szt, i, vp]
+    L.ncclDecompressReduce.argtypes = [vp, vp, szt, i, szt, i, szt, i, vp]
+    L.ncclDecompReduceComp.argtypes = [vp, ctypes.POINTER(vp), szt, i, szt, i, ctypes.POINTER(szt), ctypes.POINTER(i), szt, i, vp]
+    stream = vp(torch.cuda.current_stream().cuda_stream)
+    F32, U8, chunks, per, eb = 7, 1, 3, 8192, 2.0 ** -10
+    x = torch.randn(chunks, per, generator=torch.Generator().manual_seed(3)).cumsum(-1).mul_(0.02).cuda()
+    stride = L.ncclCompressedChunkBytes(per, F32)
+    assert stride > 16
+    comp = torch.zeros(stride * chunks, dtype=torch.uint8, device="cuda")
+    p, cc, cd = vp(comp.data_ptr()), szt(0), i(-1)
+    assert L.ncclCompress(x.data_ptr(), ctypes.byref(p), per, F32, ctypes.byref(cc), ctypes.byref(cd), chunks, 0, 4, stream) == 0
+    assert cc.value == stride and cd.value == U8
+    out = torch.empty_like(x)
+    assert L.ncclDecompress(out.data_ptr(), comp.data_ptr(), per, F32, stride, U8, chunks, 4, stream) == 0
+    acc = torch.full_like(x, 1.0)
+    assert L.ncclDecompressReduce(acc.data_ptr(), comp.data_ptr(), stride, U8, per, F32, chunks, 2, stream) == 0
+    q, rc, rd = vp(None), szt(0), i(-1)
+    assert L.ncclDecompReduceComp(comp.data_ptr(), ctypes.byref(q), per, F32, stride, U8, ctypes.byref(rc), ctypes.byref(rd), chunks, 2, stream) == 0
+    one = torch.empty(per, device="cuda")
+    assert L.ncclDecompress(one.data_ptr(), q, per, F32, rc.value, U8, 1, 2, stream) == 0
+    torch.cuda.synchronize()
+    assert (out - x).abs().max().item() <= eb
+    assert torch.equal(acc, out + 1.0)
+    assert (one - out.sum(0)).abs().max().item() <= eb * 1.001
+    stream_bytes = comp.view(chunks, stride)[:, :4].contiguous().view(torch.int32).flatten().tolist()
+    assert all(0 < b < per * 4 for b in stream_bytes), stream_bytes   # [u32 stream_bytes] and it is smaller than the raw chunk
