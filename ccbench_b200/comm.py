@@ -341,6 +341,32 @@ class Communicator:
                                   self._dtype(st), _code(codec, K.CODECS), self._stream()))
         return recv
 
+    # ---- point to point over the peer arenas -------------------------------------
+    def p2p(self, ops) -> None:
+        """ops: iterable of ("send" | "recv", tensor, peer). All of them are launched
+        together (one kernel per 16), like the content of an ncclGroupStart/End: a rank
+        may send and receive at once. Tensors of any dtype, contiguous; the byte counts of a
+        send and of its receive must match."""
+        ops = list(ops)
+        arr = (_P2pOp * len(ops))()
+        for i, (kind, t, peer) in enumerate(ops):
+            if kind not in ("send", "recv"):
+                raise ValueError(f"p2p operation {kind!r}")
+            if not t.is_cuda or not t.is_contiguous():
+                raise ValueError("p2p tensors must be contiguous CUDA tensors")
+            arr[i] = _P2pOp(t.data_ptr(), t.numel() * t.element_size(), int(peer), 1 if kind == "recv" else 0)
+        _check(lib().ccb_p2p(self._h, arr, len(ops), self._stream()))
+
+    def send(self, t: torch.Tensor, peer: int) -> None:
+        self.p2p([("send", t, peer)])
+
+    def recv(self, t: torch.Tensor, peer: int) -> None:
+        self.p2p([("recv", t, peer)])
+
+
+class _P2pOp(ctypes.Structure):
+    _fields_ = [("buf", ctypes.c_void_p), ("bytes", ctypes.c_uint64), ("peer", ctypes.c_int), ("is_recv", ctypes.c_int)]
+
 
 def _check(rc: int) -> None:
     if rc != K.OK:

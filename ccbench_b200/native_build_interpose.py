@@ -17,6 +17,9 @@ def build(verbose: bool = False) -> None:
     rpath = ["-Wl,-rpath,$ORIGIN"]
     nb.cc(libs / "libccb_nccl.so", [root / "csrc/interpose/ccb_nccl_interpose.c"], shared=True,
           libs=[str(dst), *nb.cuda_libs(), "-ldl", "-lpthread", *rpath], verbose=verbose)
+    # NCCL's API on libccb alone (no libnccl underneath): the role of the reference's NCCL-replacement wrapper
+    nb.cc(libs / "libccb_nccl_standalone.so", [root / "csrc/interpose/ccb_nccl_standalone.c"], shared=True,
+          libs=[str(dst), *nb.cuda_libs(), "-lpthread", *rpath], verbose=verbose)
     for name, src, extra in [
         ("libnccl_compress_tools.so", root / "csrc/wrappers/nccl_compress_tools.c", [*nb.cuda_libs(), "-lnccl"]),
         ("libccb_coccl_hooks.so", root / "csrc/wrappers/coccl_hooks.c", [str(dst), *nb.cuda_libs(), *rpath]),

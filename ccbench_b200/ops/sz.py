@@ -60,6 +60,13 @@ def broadcast(comm: Communicator, send, recv, eb: float, root: int = 0, used: to
     return _collective(comm, send, recv, eb, root, used)
 
 
+def launch_path() -> int:
+    """How the last collective launch went: 1 = cluster + cooperative attributes accepted
+    together, 2 = the driver refused the pair and the cluster attribute was used alone, 0 =
+    no collective launched yet."""
+    return int(_decl().ccb_sz_launch_path())
+
+
 def _collective(comm, send, recv, eb, root, used):
     sp, st = comm._ptrs(send, "send")
     rp, _ = comm._ptrs(recv, "recv")

@@ -141,6 +141,23 @@ __global__ void __launch_bounds__(kSaThreads) refwire_decode_kernel(const float*
     out[i] = Elem<T>::from_f((float)q[i] * (1.0f / scales[i / group]));
 }
 
+// out[i] = op over p of parts[p * stride + i], for the element types the fused collectives
+// do not carry (integers, double): the reduce step of the NCCL-free provider, which gathers
+// the ranks' buffers first. op: CCB_OP_*, 4 = average (sum, then divided by nparts).
+template <class T>
+__global__ void __launch_bounds__(kSaThreads) fold_kernel(const T* __restrict__ parts, size_t stride, int nparts, size_t count, int op,
+                                                          T* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+    T acc = parts[i];
+    for (int p = 1; p < nparts; ++p) {
+      const T v = parts[(size_t)p * stride + i];
+      acc = op == CCB_OP_PROD ? (T)(acc * v) : op == CCB_OP_MAX ? (v > acc ? v : acc) : op == CCB_OP_MIN ? (v < acc ? v : acc) : (T)(acc + v);
+    }
+    if (op == 4) acc = (T)(acc / (T)nparts);
+    out[i] = acc;
+  }
+}
+
 static int sa_grid(size_t units) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -313,6 +330,26 @@ extern "C" int ccb_reduce_recode(int codec, const void* const* wires, int nwires
     default: return CCB_ERR_UNSUPPORTED;
   }
   return finish("ccb_reduce_recode");
+}
+
+extern "C" int ccb_fold(int xtype, int op, const void* parts, uint64_t stride, int nparts, uint64_t count, void* out, void* stream) {
+  if (!count) return CCB_OK;
+  if (nparts < 1 || op < 0 || op > 4) return CCB_ERR_ARG;
+  const int g = sa_grid((count + 31) / 32);  // one thread per element, grid-stride beyond the cap
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define CCB_FOLD(T) fold_kernel<T><<<g, kSaThreads, 0, s>>>((const T*)parts, stride, nparts, count, op, (T*)out)
+  switch (xtype) {
+    case CCB_X_I8: CCB_FOLD(int8_t); break;
+    case CCB_X_U8: CCB_FOLD(uint8_t); break;
+    case CCB_X_I32: CCB_FOLD(int32_t); break;
+    case CCB_X_U32: CCB_FOLD(uint32_t); break;
+    case CCB_X_I64: CCB_FOLD(long long); break;
+    case CCB_X_U64: CCB_FOLD(unsigned long long); break;
+    case CCB_X_F64: CCB_FOLD(double); break;
+    default: return CCB_ERR_UNSUPPORTED;
+  }
+#undef CCB_FOLD
+  return finish("ccb_fold");
 }
 
 // Reference wire v0 (see the file comment). `wire` holds ceil(count/group) floats then count int8.

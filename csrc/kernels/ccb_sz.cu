@@ -628,6 +628,10 @@ static void fill_geometry(SzArgs& a, int nx, int ny, int nz, float eb) {
   a.inv_two_eb = 1.f / a.two_eb;
 }
 
+// How the last waiting launch went: 1 = cluster + cooperative accepted, 2 = refused and
+// launched with the cluster attribute alone (co-residency then rests on the occupancy bound).
+static int g_sz_launch_path = 0;
+
 // Launch with a cluster of 8 CTAs; cooperative when the kernel waits on peers.
 static int sz_launch(SzArgs& a, int nlocal, int num_sms, bool waits, cudaStream_t stream) {
   void (*kernel)(const SzArgs) = a.mode == 0 ? sz_kernel<0> : a.mode == 1 ? sz_kernel<1> : sz_kernel<2>;
@@ -661,9 +665,11 @@ static int sz_launch(SzArgs& a, int nlocal, int num_sms, bool waits, cudaStream_
     cfg.numAttrs = 2;
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, a);
+  if (waits) g_sz_launch_path = 1;
   if (e != cudaSuccess && waits) {  // some drivers refuse cluster + cooperative: the bounded grid still fits
     (void)cudaGetLastError();
     cfg.numAttrs = 1;
+    g_sz_launch_path = 2;
     e = cudaLaunchKernelEx(&cfg, kernel, a);
   }
   if (e != cudaSuccess) {
@@ -684,6 +690,8 @@ static int device_sms() {
 }  // namespace ccb
 
 using namespace ccb;
+
+extern "C" int ccb_sz_launch_path(void) { return g_sz_launch_path; }
 
 extern "C" uint64_t ccb_sz_capacity(int nx, int ny, int nz) {
   SzArgs a;

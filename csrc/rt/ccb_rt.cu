@@ -673,17 +673,38 @@ extern "C" int ccb_all_reduce_symm(ccb_comm* c, uint64_t send_off, uint64_t recv
 // ---- point-to-point over the peer arenas --------------------------------------------------
 // ops: `nops` sends and receives of THIS rank, all launched as one kernel (what an
 // ncclGroupStart/End holds, or one call). Message sizes must match at the two ends.
+static int p2p_flush(ccb_comm* c, P2pArgs& a, cudaStream_t stream) {
+  if (a.nops == 0) return CCB_OK;
+  dim3 grid(kP2pLanes, (unsigned)a.nops, 1), block(kThreads, 1, 1);
+  void* params[] = {&a};
+  // the lanes of one operation do not wait on each other, and the two ends of a transfer
+  // run on different GPUs: a plain launch is enough
+  cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(&p2p_kernel), grid, block, params, 0, stream);
+  a.nops = 0;
+  if (e != cudaSuccess) {
+    set_error("p2p launch failed: %s", cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  count_launch();
+  return CCB_OK;
+}
 extern "C" int ccb_p2p(ccb_comm* c, const ccb_p2p_op* ops, int nops, ccb_stream_t stream_) {
   int rc = check_alive(c);
   if (rc) return rc;
-  if (!ops || nops < 1 || nops > kP2pMaxOps) {
-    set_error("ccb_p2p takes 1 to %d operations per call", kP2pMaxOps);
+  if (!ops || nops < 1) {
+    set_error("ccb_p2p: no operations");
     return CCB_ERR_ARG;
   }
   if (!c->p2p_offset) {
     set_error("this communicator has no point-to-point mailboxes (one rank per process and an arena of at least 64 MiB are needed)");
     return CCB_ERR_UNSUPPORTED;
   }
+  for (int i = 0; i < nops; ++i)
+    if (ops[i].peer < 0 || ops[i].peer >= c->nranks || ops[i].peer == c->rank0 || (!ops[i].buf && ops[i].bytes)) {
+      set_error("ccb_p2p: bad peer %d or null buffer", ops[i].peer);
+      return CCB_ERR_ARG;
+    }
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   P2pArgs a;
   memset(&a, 0, sizeof(a));
   a.c = comm_dev(c, c->epoch ? c->epoch : 1);   // point-to-point does not advance the collectives' epoch
@@ -691,36 +712,25 @@ extern "C" int ccb_p2p(ccb_comm* c, const ccb_p2p_op* ops, int nops, ccb_stream_
   a.lane_bytes = c->p2p_lane_bytes;
   a.rank = c->rank0;
   const size_t round_bytes = (size_t)kP2pLanes * c->p2p_lane_bytes;
-  int k = 0;
   for (int i = 0; i < nops; ++i) {
     const ccb_p2p_op& o = ops[i];
-    if (o.peer < 0 || o.peer >= c->nranks || o.peer == c->rank0 || (!o.buf && o.bytes)) {
-      set_error("ccb_p2p: bad peer %d or null buffer", o.peer);
-      return CCB_ERR_ARG;
-    }
     if (o.bytes == 0) continue;
+    // Two transfers of one direction between one pair share mailboxes and counters: the
+    // second goes into a later launch (both ends split at the same place, since they see
+    // the same sequence for the pair). A full batch is launched too.
+    bool clash = a.nops == kP2pMaxOps;
+    for (int k = 0; k < a.nops && !clash; ++k) clash = a.op[k].peer == o.peer && a.op[k].is_recv == (o.is_recv ? 1 : 0);
+    if (clash && (rc = p2p_flush(c, a, stream)) != CCB_OK) return rc;
     unsigned int* ctr = o.is_recv ? &c->p2p_rcvd[o.peer] : &c->p2p_sent[o.peer];
-    a.op[k].buf = o.buf;
-    a.op[k].bytes = o.bytes;
-    a.op[k].peer = o.peer;
-    a.op[k].is_recv = o.is_recv ? 1 : 0;
-    a.op[k].first_round = *ctr;
+    P2pOp& d = a.op[a.nops++];
+    d.buf = o.buf;
+    d.bytes = o.bytes;
+    d.peer = o.peer;
+    d.is_recv = o.is_recv ? 1 : 0;
+    d.first_round = *ctr;
     *ctr += (unsigned int)((o.bytes + round_bytes - 1) / round_bytes);
-    ++k;
   }
-  if (k == 0) return CCB_OK;
-  a.nops = k;
-  dim3 grid(kP2pLanes, (unsigned)k, 1), block(kThreads, 1, 1);
-  void* params[] = {&a};
-  // the lanes of one operation do not wait on each other, and the two ends of a transfer
-  // run on different GPUs: a plain launch is enough
-  cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(&p2p_kernel), grid, block, params, 0, static_cast<cudaStream_t>(stream_));
-  if (e != cudaSuccess) {
-    set_error("p2p launch failed: %s", cudaGetErrorString(e));
-    return CCB_ERR_CUDA;
-  }
-  count_launch();
-  return CCB_OK;
+  return p2p_flush(c, a, stream);
 }
 extern "C" int ccb_send(ccb_comm* c, const void* buf, uint64_t bytes, int peer, ccb_stream_t stream) {
   ccb_p2p_op o = {const_cast<void*>(buf), bytes, peer, 0};

@@ -81,8 +81,10 @@ uint64_t ccb_wire_bytes(int codec, int dtype, uint64_t count);
 /* ---- point-to-point ----------------------------------------------------------------
  * Sends and receives over the peer arenas, no NCCL involved: the sender stores into a
  * mailbox in the receiver's arena, the receiver copies out. ccb_p2p launches the
- * operations of one rank (at most 16: the content of one ncclGroupStart/End) as ONE
- * kernel, so a rank may send and receive at the same time. The byte counts of a send and
+ * operations of one rank (the content of one ncclGroupStart/End) as ONE kernel per 16
+ * operations, so a rank may send and receive at the same time; a second transfer of the
+ * same direction to the same peer starts a new kernel. Transfers between a pair must be
+ * issued in the same order at both ends and on one stream (or otherwise ordered). The byte counts of a send and
  * of the matching receive must be equal; transfers between a pair are matched in issue
  * order. A send of up to two rounds (2 x 16 x lane bytes, 8 MiB with the default arena)
  * completes without its receive being posted, longer ones wait for it (bounded). */
@@ -152,6 +154,10 @@ int ccb_decode_chunks(int codec, int dtype, const void* wire, uint64_t wire_stri
                       void* out, int accumulate, ccb_stream_t stream);
 /* inout += src, element-wise in the element type. */
 int ccb_accumulate(int dtype, const void* src, void* inout, uint64_t count, ccb_stream_t stream);
+/* out[i] = op over p < nparts of parts[p * stride + i] for the CCB_X_* element types (integers and
+ * double); op is a CCB_OP_* value or 4 for the average. Used by the NCCL-free provider, which
+ * gathers the ranks' buffers and folds them locally for types the fused kernels do not carry. */
+int ccb_fold(int xtype, int op, const void* parts, uint64_t stride, int nparts, uint64_t count, void* out, ccb_stream_t stream);
 /* wire_out = encode(sum_k decode(wires[k])), 1 <= nwires <= 16 */
 int ccb_reduce_recode(int codec, const void* const* wires, int nwires, uint64_t count, void* wire_out,
                       ccb_stream_t stream);

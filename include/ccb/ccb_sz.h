@@ -18,6 +18,10 @@ extern "C" {
 /* Bytes a compressed buffer must provide for an nx*ny*nz field (fixed-capacity group
  * slots; the bytes actually used are reported by ccb_sz_compress). */
 uint64_t ccb_sz_capacity(int nx, int ny, int nz);
+/* How the last collective launch of this process went: 0 = none yet, 1 = the driver took the
+ * cluster and the cooperative attribute together, 2 = it refused the pair and the kernel was
+ * launched with the cluster attribute alone (grid bounded by the resident-cluster count). */
+int ccb_sz_launch_path(void);
 /* |in - decompress(compress(in))| <= eb for every finite element. `d_used` (device
  * memory, optional) receives the number of compressed bytes produced. */
 int ccb_sz_compress(const float* in, int nx, int ny, int nz, float eb, void* out, unsigned long long* d_used,

@@ -41,6 +41,8 @@ enum {
   CCB_CODEC_INT4 = 4      /* int4, fp32 scale = absmax/7 per 128 values       */
 };
 enum { CCB_OP_SUM = 0, CCB_OP_PROD = 1, CCB_OP_MAX = 2, CCB_OP_MIN = 3 };
+/* element types of ccb_fold only (the fused collectives carry CCB_F32 / CCB_F16 / CCB_BF16) */
+enum { CCB_X_I8 = 16, CCB_X_U8 = 17, CCB_X_I32 = 18, CCB_X_U32 = 19, CCB_X_I64 = 20, CCB_X_U64 = 21, CCB_X_F64 = 22 };
 /* AllReduce algorithms. */
 enum { CCB_ALGO_AUTO = 0, CCB_ALGO_TWOSHOT = 1, CCB_ALGO_ONESHOT = 2, CCB_ALGO_RING = 3, CCB_ALGO_TREE = 4, CCB_ALGO_NVLS = 5 };
 

@@ -118,6 +118,7 @@ def _body(comm, rank, world, dev):
     assert comm.status()[0] == 0
     _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs)
     _sz_and_moe(comm, rank, world, dev, gather_inputs)
+    _point_to_point(comm, rank, world, dev)
 
 
 def _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs):
@@ -202,6 +203,43 @@ def _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs):
     assert comm.status()[0] == 0
 
 
+def _point_to_point(comm, rank, world, dev):
+    """Sends and receives over the arena mailboxes: a ring shift in one grouped launch, odd
+    byte counts and unaligned starts, a message of many rounds, and two messages to the same
+    peer in one call (which the runtime puts into consecutive launches)."""
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+
+    def payload(r, n, salt):
+        return (torch.arange(n, dtype=torch.int64) * (2 * r + 3) + salt).to(torch.uint8)
+
+    for n, salt in ((1, 1), (4099, 2), (1 << 20, 3), ((48 << 20) + 7, 4)):
+        mine = payload(rank, n + 3, salt).to(dev)
+        got = torch.zeros(n + 5, dtype=torch.uint8, device=dev)
+        comm.p2p([("send", mine[3:], nxt), ("recv", got[5:], prv)])   # starts off a 16-byte boundary
+        torch.cuda.synchronize()
+        assert comm.status()[0] == 0, comm.status()
+        assert torch.equal(got[5:].cpu(), payload(prv, n + 3, salt)[3:]), ("p2p ring", n)
+        assert int(got[:5].sum()) == 0
+    a, b = payload(rank, 70001, 5).to(dev), payload(rank, 333, 6).to(dev)
+    ra, rb = torch.zeros(70001, dtype=torch.uint8, device=dev), torch.zeros(333, dtype=torch.uint8, device=dev)
+    comm.p2p([("send", a, nxt), ("send", b, nxt), ("recv", ra, prv), ("recv", rb, prv)])
+    torch.cuda.synchronize()
+    assert torch.equal(ra.cpu(), payload(prv, 70001, 5)) and torch.equal(rb.cpu(), payload(prv, 333, 6))
+    # everyone to everyone in one launch (float payload)
+    x = torch.full((world, 5000), float(rank), device=dev) + torch.arange(world, device=dev)[:, None] * 0.5
+    y = torch.zeros_like(x)
+    ops = []
+    for p in range(world):
+        if p != rank:
+            ops += [("send", x[p], p), ("recv", y[p], p)]
+    comm.p2p(ops)
+    torch.cuda.synchronize()
+    for p in range(world):
+        if p != rank:
+            assert torch.equal(y[p].cpu(), torch.full((5000,), float(p)) + rank * 0.5), ("p2p all pairs", p)
+    assert comm.status()[0] == 0
+
+
 def _sz_and_moe(comm, rank, world, dev, gather_inputs):
     """Error-bounded AllGather / Broadcast and MoE dispatch + combine over real peers."""
     from ccbench_b200.models.workloads import moe_routing, smooth_field
@@ -214,8 +252,10 @@ def _sz_and_moe(comm, rank, world, dev, gather_inputs):
     eb = 1e-3 * max((f.max() - f.min()).item() for f in flds)
     eb32 = float(torch.tensor(eb, dtype=torch.float32))
     recv = torch.zeros((world, n, n, n), device=dev)
-    for _ in range(3):
+    for it in range(3):
         sz.all_gather(comm, fld, recv, eb)
+        if rank == 0 and it == 0:
+            print("sz launch path:", sz.launch_path(), "(1 = cluster + cooperative, 2 = cluster alone)", flush=True)
     torch.cuda.synchronize()
     assert comm.status()[0] == 0
     for q in range(world):
