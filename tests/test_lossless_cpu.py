@@ -42,3 +42,21 @@ def test_gradient_like_data_shrinks():
     const = torch.full((8192,), 1.5, dtype=torch.bfloat16)
     r = 8192 * 2 / LL.used_bytes_np(LL.np_encode(_bits(const), 1))
     assert r > 1.9   # no exponent planes at all
+
+
+def test_ratio_tool_on_the_numpy_codec(tmp_path, capsys):
+    """The ratio measurement over dataset files (the role of the reference's lossless-codec
+    scripts), on the NumPy codec: smooth-exponent data compresses, the table has one row per
+    (file, size) and stops at the file's size."""
+    import numpy as np
+
+    from ccbench_b200.bench import lossless_ratio as R
+
+    rng = np.random.default_rng(0)
+    (rng.standard_normal(40000).astype(np.float32) * 1e-3).tofile(tmp_path / "grad.f32")
+    (1.0 + rng.random(30000)).astype(np.float16).tofile(tmp_path / "act.f16")
+    rows = R.run(sorted(tmp_path.iterdir()), [65536, 1 << 20], on_gpu=False)
+    assert [(r["dataset"], r["bytes"]) for r in rows] == [("act", 60000), ("grad", 65536), ("grad", 160000)]
+    assert all(0.5 < r["ratio"] < 1.0 for r in rows), rows
+    assert R.main([str(tmp_path), "--cpu", "--sizes", "64K"]) == 0
+    assert "ratio below 1.0" in capsys.readouterr().out
