@@ -9,6 +9,9 @@ process. `python -m ccbench_b200.bench.cases --case NAME [--launches 3]`.
   moe_dispatch_fp8       4096 tokens x 4096 hidden bf16, 4 ranks on this GPU
   allreduce_ring_int8_8ranks   ring kernel, eight ranks on this GPU, 16 Mi bf16 each
   allgather_fp8_8ranks   exchange kernel, eight ranks on this GPU, 4 Mi bf16 each
+  allreduce_pipe_int8_4ranks   warp-specialised two-shot kernel (1024 threads), four ranks on
+                         this GPU, 16 Mi bf16 each
+  lossless_encode / lossless_decode   lossless float codec, 128 Mi bf16 (256 MB)
 """
 from __future__ import annotations
 
@@ -50,6 +53,25 @@ def main(argv=None):
         ys = [torch.empty_like(x) for x in xs]
         for _ in range(a.launches):
             comm.all_reduce(xs, ys, codec="int8", algo="ring")
+    elif a.case == "allreduce_pipe_int8_4ranks":
+        n = 4
+        comm = Communicator.local(n, arena_bytes=96 << 20)
+        comm.set_pipeline(2)
+        xs = [gradient_like(16 << 20, torch.bfloat16, seed=r, device=dev) for r in range(n)]
+        ys = [torch.empty_like(x) for x in xs]
+        for _ in range(a.launches):
+            comm.all_reduce(xs, ys, codec="int8", algo="twoshot")
+    elif a.case in ("lossless_encode", "lossless_decode"):
+        from ..ops import lossless
+
+        x = gradient_like(128 << 20, torch.bfloat16, device=dev)
+        comp = lossless.encode(x)
+        out = torch.empty_like(x)
+        for _ in range(a.launches):
+            if a.case == "lossless_encode":
+                lossless.encode(x)
+            else:
+                lossless.decode(comp, x.numel(), x.dtype, out=out)
     elif a.case == "allgather_fp8_8ranks":
         n = 8
         comm = Communicator.local(n, arena_bytes=96 << 20)

@@ -373,8 +373,10 @@ ncclResult_t ncclAllGather(const void *sendbuff, void *recvbuff, size_t sendcoun
     return byte_exchange(comm, (const char *)sendbuff, scnt, soff, (char *)recvbuff, scnt, roff, stream);
 }
 
-ncclResult_t ncclAllToAll(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
-                          cudaStream_t stream) {
+/* The extension collectives keep the signatures of the reference's extension library
+ * (send and receive sides described separately); ncclAlltoAll is NCCL 2.28's own spelling. */
+static ncclResult_t all_to_all(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
+                               cudaStream_t stream) {
     const size_t tb = type_bytes(datatype), bytes = count * tb;
     if (!valid(comm) || tb == 0) return ncclInvalidArgument;
     if (bytes == 0) return ncclSuccess;
@@ -393,6 +395,15 @@ ncclResult_t ncclAllToAll(const void *sendbuff, void *recvbuff, size_t count, nc
     size_t scnt[CCB_MAX_RANKS], off[CCB_MAX_RANKS];
     for (int p = 0; p < comm->n; ++p) scnt[p] = bytes, off[p] = (size_t)p * bytes;
     return byte_exchange(comm, (const char *)sendbuff, scnt, off, (char *)recvbuff, scnt, off, stream);
+}
+int ncclAllToAll(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
+                 ncclDataType_t recvtype, ncclComm_t comm, cudaStream_t stream) {
+    if (sendcount * type_bytes(sendtype) != recvcount * type_bytes(recvtype)) return (int)ncclInvalidArgument;
+    return (int)all_to_all(sendbuf, recvbuf, sendcount, sendtype, comm, stream);
+}
+ncclResult_t ncclAlltoAll(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
+                          cudaStream_t stream) {
+    return all_to_all(sendbuff, recvbuff, count, datatype, comm, stream);
 }
 
 ncclResult_t ncclBroadcast(const void *sendbuff, void *recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm,
@@ -422,27 +433,29 @@ ncclResult_t ncclBcast(void *buff, size_t count, ncclDataType_t datatype, int ro
     return ncclBroadcast(buff, buff, count, datatype, root, comm, stream);
 }
 
-ncclResult_t ncclScatter(const void *sendbuff, void *recvbuff, size_t recvcount, ncclDataType_t datatype, int root, ncclComm_t comm,
-                         cudaStream_t stream) {
-    const size_t tb = type_bytes(datatype), bytes = recvcount * tb;
-    if (!valid(comm) || tb == 0 || root < 0 || root >= comm->n) return ncclInvalidArgument;
-    if (bytes == 0) return ncclSuccess;
+int ncclScatter(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
+                ncclDataType_t recvtype, int root, ncclComm_t comm, cudaStream_t stream) {
+    const size_t bytes = recvcount * type_bytes(recvtype);
+    if (!valid(comm) || type_bytes(recvtype) == 0 || root < 0 || root >= comm->n) return (int)ncclInvalidArgument;
+    if (comm->rank == root && sendcount * type_bytes(sendtype) != bytes) return (int)ncclInvalidArgument;
+    if (bytes == 0) return (int)ncclSuccess;
     size_t scnt[CCB_MAX_RANKS] = {0}, soff[CCB_MAX_RANKS] = {0}, rcnt[CCB_MAX_RANKS] = {0}, zero[CCB_MAX_RANKS] = {0};
     if (comm->rank == root)
         for (int p = 0; p < comm->n; ++p) scnt[p] = bytes, soff[p] = (size_t)p * bytes;
     rcnt[root] = bytes;
-    return byte_exchange(comm, (const char *)sendbuff, scnt, soff, (char *)recvbuff, rcnt, zero, stream);
+    return (int)byte_exchange(comm, (const char *)sendbuf, scnt, soff, (char *)recvbuf, rcnt, zero, stream);
 }
-ncclResult_t ncclGather(const void *sendbuff, void *recvbuff, size_t sendcount, ncclDataType_t datatype, int root, ncclComm_t comm,
-                        cudaStream_t stream) {
-    const size_t tb = type_bytes(datatype), bytes = sendcount * tb;
-    if (!valid(comm) || tb == 0 || root < 0 || root >= comm->n) return ncclInvalidArgument;
-    if (bytes == 0) return ncclSuccess;
+int ncclGather(const void *sendbuf, size_t sendcount, ncclDataType_t sendtype, void *recvbuf, size_t recvcount,
+               ncclDataType_t recvtype, int root, ncclComm_t comm, cudaStream_t stream) {
+    const size_t bytes = sendcount * type_bytes(sendtype);
+    if (!valid(comm) || type_bytes(sendtype) == 0 || root < 0 || root >= comm->n) return (int)ncclInvalidArgument;
+    if (comm->rank == root && recvcount * type_bytes(recvtype) != bytes) return (int)ncclInvalidArgument;
+    if (bytes == 0) return (int)ncclSuccess;
     size_t scnt[CCB_MAX_RANKS] = {0}, zero[CCB_MAX_RANKS] = {0}, rcnt[CCB_MAX_RANKS] = {0}, roff[CCB_MAX_RANKS] = {0};
     scnt[root] = bytes;
     if (comm->rank == root)
         for (int p = 0; p < comm->n; ++p) rcnt[p] = bytes, roff[p] = (size_t)p * bytes;
-    return byte_exchange(comm, (const char *)sendbuff, scnt, zero, (char *)recvbuff, rcnt, roff, stream);
+    return (int)byte_exchange(comm, (const char *)sendbuf, scnt, zero, (char *)recvbuf, rcnt, roff, stream);
 }
 
 /* Reduction of a type the fused kernels do not carry: bring every rank's piece here, fold.

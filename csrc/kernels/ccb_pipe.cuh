@@ -36,6 +36,10 @@ struct PipeShared {
   unsigned int p1_ready;   // waves whose phase-1 flags from all peers have been seen
   unsigned int p2_ready;   // the same for phase 2
   int fail;
+  // kb[s][w]: first chunk (of this CTA's chunks of shard s) that belongs to wave w; computed
+  // once per launch, so that the phases do no division (a 64-bit division per phase, peer
+  // and wave cost more instructions than the data loops of a warp)
+  unsigned int kb[CCB_MAX_RANKS][CCB_MAX_SLOTS / 2 + 1];
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_cta_shared(const unsigned int* p) {
@@ -177,31 +181,36 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
   const size_t pad = a.shard_pad;
   const bool use_mc = a.use_mc && c.mc_arena != nullptr;
   const uint32_t peers = ((1u << n) - 1u) & ~(1u << r);
-  if (threadIdx.x == 0) {
-    for (int w = 0; w < CCB_MAX_SLOTS / 2; ++w) sh.p1_done[w] = sh.p2_done[w] = 0u;
-    sh.p1_ready = sh.p2_ready = 0u;
-    sh.fail = 0;
-  }
-  __syncthreads();  // the only CTA-wide barrier: the roles part ways here
-
   auto shard_valid = [&](int s) -> size_t {
     const size_t beg = (size_t)s * a.shard_elems;
     if (beg >= a.count) return 0;
     const size_t left = a.count - beg;
     return left < a.shard_elems ? left : a.shard_elems;
   };
-  // Items (512-element units) of this CTA in wave w of a shard with `valid` elements:
-  // the CTA owns chunks b, b + G, b + 2G, ... of 8 units; the wave takes a slice of them.
-  auto wave_items = [&](size_t valid, int w, size_t& kb) -> size_t {
-    const size_t units = (valid + kWarpElems - 1) / kWarpElems;
-    const size_t nch = (units + kPipeChunkUnits - 1) >> kPipeChunkShift;
-    const size_t K = nch > b ? (nch - b + G - 1) / G : 0;
-    kb = K * (size_t)w / W;
-    return (K * (size_t)(w + 1) / W - kb) << kPipeChunkShift;
+  if (threadIdx.x == 0) {
+    for (int w = 0; w < CCB_MAX_SLOTS / 2; ++w) sh.p1_done[w] = sh.p2_done[w] = 0u;
+    sh.p1_ready = sh.p2_ready = 0u;
+    sh.fail = 0;
+  }
+  // Items are 512-element units; the CTA owns chunks b, b + G, b + 2G, ... of 8 units of every
+  // shard, and wave w takes the slice [kb[s][w], kb[s][w + 1]) of them. 32-bit arithmetic: a
+  // shard has fewer than 2^32 units.
+  if (threadIdx.x >= 32 && threadIdx.x < 32 + (unsigned)n) {
+    const int s = threadIdx.x - 32;
+    const unsigned int units = (unsigned int)((shard_valid(s) + kWarpElems - 1) / kWarpElems);
+    const unsigned int nch = (units + kPipeChunkUnits - 1) >> kPipeChunkShift;
+    const unsigned int K = nch > (unsigned int)b ? (nch - (unsigned int)b + (unsigned int)G - 1u) / (unsigned int)G : 0u;
+    for (int w = 0; w <= W; ++w) sh.kb[s][w] = (unsigned int)((unsigned long long)K * (unsigned)w / (unsigned)W);
+  }
+  __syncthreads();  // the only CTA-wide barrier: the roles part ways here
+
+  auto wave_items = [&](int s, int w, unsigned int& kb) -> unsigned int {
+    kb = sh.kb[s][w];
+    return (sh.kb[s][w + 1] - kb) << kPipeChunkShift;
   };
-  auto item_elem = [&](size_t kb, size_t i) -> size_t {
-    const size_t ch = b + (kb + (i >> kPipeChunkShift)) * G;
-    return ((ch << kPipeChunkShift) + (i & (kPipeChunkUnits - 1))) * kWarpElems;
+  auto item_elem = [&](unsigned int kb, unsigned int i) -> size_t {
+    const unsigned int ch = (unsigned int)b + (kb + (i >> kPipeChunkShift)) * (unsigned int)G;
+    return (size_t)((ch << kPipeChunkShift) + (i & (kPipeChunkUnits - 1))) * kWarpElems;
   };
 
   const bool sum = (a.op == CCB_OP_SUM);
@@ -218,19 +227,26 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
   // ---- phase 1 of wave w: this rank's lanes of every peer's shard, to the owner ----
   auto phase1 = [&](int w, int gw, int gn) {
     for (int j = 1; j < n; ++j) {
-      const int p = (r + j) % n;
+      const int p = r + j < n ? r + j : r + j - n;
       const size_t valid = shard_valid(p);
       const T* src = send + (size_t)p * a.shard_elems;
       float* efs = ef ? ef + (size_t)p * a.shard_elems : nullptr;
       char* dst = c.arena[p] + area1 + (size_t)r * a.slot_bytes;
-      size_t kb;
-      const size_t items = wave_items(valid, w, kb);
-      for (size_t i = gw; i < items; i += gn) {
-        const size_t e0 = item_elem(kb, i);
-        if (e0 >= valid) continue;
+      unsigned int kb;
+      const unsigned int items = wave_items(p, w, kb);
+      // The raw elements of the next item are requested before the current one is encoded,
+      // so a warp has two loads in flight instead of a load and then an idle wait.
+      Raw16<T> raw;
+      unsigned int i = gw;
+      size_t e0 = i < items ? item_elem(kb, i) : valid;
+      if (e0 < valid) load16_raw<T>(src, e0 + lane * kLaneElems, valid, raw);
+      while (e0 < valid) {
         const size_t idx = e0 + lane * kLaneElems;
         float v[16];
-        load16<T>(src, idx, valid, v);
+        raw16_to_f<T>(raw, v);
+        i += gn;
+        e0 = i < items ? item_elem(kb, i) : valid;
+        if (e0 < valid) load16_raw<T>(src, e0 + lane * kLaneElems, valid, raw);
         if (efs) {
           float e[16];
           load16f_plain(efs, idx, valid, e);
@@ -257,18 +273,22 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
     const T* src = send + (size_t)r * a.shard_elems;
     float* efs = (ef && ar) ? ef + (size_t)r * a.shard_elems : nullptr;
     T* out = ar ? recv + (size_t)r * a.shard_elems : recv;
-    size_t kb;
-    const size_t items = wave_items(valid, w, kb);
-    for (size_t i = gw; i < items; i += gn) {
+    unsigned int kb;
+    const unsigned int items = wave_items(r, w, kb);
+    for (unsigned int i = gw; i < items; i += gn) {
       const size_t e0 = item_elem(kb, i);
       if (e0 >= valid) continue;
       const size_t idx = e0 + lane * kLaneElems;
+      // The packet of the next source is requested before the current one is decoded.
+      typename C::Packet nxt;
+      int q = (r == 0) ? 1 : 0;
+      C::load(my + area1 + (size_t)q * a.slot_bytes, pad, idx, nxt);
       float acc[16];
       load16<T>(src, idx, valid, acc);
-      for (int q = 0; q < n; ++q) {  // increasing rank order, as in reduce_kernel
-        if (q == r) continue;
-        typename C::Packet pk;
-        C::load(my + area1 + (size_t)q * a.slot_bytes, pad, idx, pk);
+      while (q < n) {  // increasing rank order, as in reduce_kernel
+        const typename C::Packet pk = nxt;
+        q += (q + 1 == r) ? 2 : 1;
+        if (q < n) C::load(my + area1 + (size_t)q * a.slot_bytes, pad, idx, nxt);
         float d[16];
         C::decode(pk, d);
         accumulate(acc, d);
@@ -288,7 +308,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
       if (use_mc) {
         C::store_mc(c.mc_arena + area2 + (size_t)r * a.slot_bytes, pad, idx, pk);
       } else {
-        for (int j = 1; j < n; ++j) C::store(c.arena[(r + j) % n] + area2 + (size_t)r * a.slot_bytes, pad, idx, pk);
+        for (int j = 1; j < n; ++j) C::store(c.arena[r + j < n ? r + j : r + j - n] + area2 + (size_t)r * a.slot_bytes, pad, idx, pk);
       }
       float d[16];
       C::decode(pk, d);
@@ -305,20 +325,25 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
   // ---- phase 3 of wave w: decode the peers' reduced shards ----
   auto phase3 = [&](int w, int gw, int gn) {
     for (int j = 1; j < n; ++j) {
-      const int q = (r + j) % n;
+      const int q = r + j < n ? r + j : r + j - n;
       const size_t valid = shard_valid(q);
       const char* slot = my + area2 + (size_t)q * a.slot_bytes;
       T* out = recv + (size_t)q * a.shard_elems;
-      size_t kb;
-      const size_t items = wave_items(valid, w, kb);
-      for (size_t i = gw; i < items; i += gn) {
-        const size_t e0 = item_elem(kb, i);
-        if (e0 >= valid) continue;
-        typename C::Packet pk;
-        C::load(slot, pad, e0 + lane * kLaneElems, pk);
+      unsigned int kb;
+      const unsigned int items = wave_items(q, w, kb);
+      typename C::Packet nxt;
+      unsigned int i = gw;
+      size_t e0 = i < items ? item_elem(kb, i) : valid;
+      if (e0 < valid) C::load(slot, pad, e0 + lane * kLaneElems, nxt);
+      while (e0 < valid) {
+        const size_t idx = e0 + lane * kLaneElems;
+        const typename C::Packet pk = nxt;
+        i += gn;
+        e0 = i < items ? item_elem(kb, i) : valid;
+        if (e0 < valid) C::load(slot, pad, e0 + lane * kLaneElems, nxt);
         float d[16];
         C::decode(pk, d);
-        store16<T>(out, e0 + lane * kLaneElems, valid, d);
+        store16<T>(out, idx, valid, d);
       }
     }
   };

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
       typename C::Packet pk;
       C::encode(v, pk);
       for (int j = 0; j < n; ++j) {
-        const int p = (r + j) % n;
+        const int p = r + j < n ? r + j : r + j - n;
         C::store(c.arena[p] + area1 + (size_t)r * a.slot_bytes, pad, idx, pk);
       }
       if (ef) {
@@ -156,16 +156,24 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
   } else {
     const int W = a.waves < 1 ? 1 : a.waves;
     // k-range of this CTA's tiles (t = b + k*G) of a shard that belong to wave w
+    // 32-bit arithmetic (a shard has fewer than 2^32 tiles): a 64-bit division costs about a
+    // hundred instructions, and this runs per phase, peer and wave
     auto wave_range = [&](size_t valid, int w, size_t& kb, size_t& ke) {
-      const size_t nt = (valid + tile_elems - 1) / tile_elems;
-      const size_t K = nt > (size_t)b ? (nt - b + G - 1) / G : 0;
-      kb = K * (size_t)w / W;
-      ke = K * (size_t)(w + 1) / W;
+      const unsigned int units = (unsigned int)((valid + kWarpElems - 1) / kWarpElems);  // constant divisor: a shift
+      const unsigned int nt = (units + (unsigned int)a.tile_warps - 1u) / (unsigned int)a.tile_warps;
+      const unsigned int K = nt > (unsigned int)b ? (nt - (unsigned int)b + (unsigned int)G - 1u) / (unsigned int)G : 0u;
+      if (W == 1) {
+        kb = 0;
+        ke = K;
+      } else {
+        kb = K * (unsigned int)w / (unsigned int)W;
+        ke = K * (unsigned int)(w + 1) / (unsigned int)W;
+      }
     };
 
     auto phase1 = [&](int w) {
       for (int j = 1; j < n; ++j) {
-        const int p = (r + j) % n;
+        const int p = r + j < n ? r + j : r + j - n;
         if (rooted && p != a.root) continue;
         const int s = rooted ? 0 : p;
         const size_t valid = shard_valid(s);
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
           typename C::Packet pk;
           C::encode(acc, pk);
           for (int j = 1; j < n; ++j) {
-            const int p = (r + j) % n;
+            const int p = r + j < n ? r + j : r + j - n;
             C::store(c.arena[p] + area2 + (size_t)r * a.slot_bytes, pad, idx, pk);
           }
           float d[16];
@@ -264,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 2) reduce_kernel(const __grid_consta
     auto phase3 = [&](int w) -> bool {
       if (!cta_wait_sources(sync, c, my, 2 * w + 1, r, 0xffu, 0x20 | (w << 16))) return false;
       for (int j = 1; j < n; ++j) {
-        const int q = (r + j) % n;
+        const int q = r + j < n ? r + j : r + j - n;
         const size_t valid = shard_valid(q);
         size_t kb, ke;
         wave_range(valid, w, kb, ke);

@@ -42,6 +42,8 @@ COLLECTIVES = ["allreduce", "allgather", "allgatherv", "alltoall", "bcast", "red
 
 @pytest.mark.parametrize("test", COLLECTIVES)
 def test_float_collectives_are_exact_without_a_codec(tmp_path, test):
+    if test in ("allgatherv", "scatterv") and _ranks() < 2:
+        pytest.skip("this driver wants at least two ranks")
     out = _run(tmp_path, test, ["-L", "4096,1048576", "-i", "2", "-w", "1", "-d", "float", "-p", "rank_linear", "-v", "-t", "1e30",
                                 "-e", "rel_l2"])
     assert max(_metric(out, "rel_l2")) < 1e-6
