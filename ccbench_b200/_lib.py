@@ -85,6 +85,7 @@ def _declare(L: ctypes.CDLL) -> None:
     L.ccb_wire_bytes.argtypes = [c_int, c_int, c_u64]
     L.ccb_wire_bytes.restype = c_u64
     L.ccb_p2p.argtypes = [c_vp, c_vp, c_int, c_vp]
+    L.ccb_link_probe.argtypes = [c_vp, c_int, c_int, c_u64, c_vp]
     L.ccb_fold.argtypes = [c_int, c_int, c_vp, c_u64, c_int, c_u64, c_vp, c_vp]
     L.ccb_all_reduce.argtypes = [c_vp, pp, pp, c_u64, c_int, c_int, c_int, c_int, pp, c_vp]
     L.ccb_reduce_scatter.argtypes = [c_vp, pp, pp, c_u64, c_int, c_int, c_int, pp, c_vp]

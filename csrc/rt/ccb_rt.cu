@@ -21,6 +21,7 @@
 #include "../kernels/ccb_exchange.cuh"
 #include "../kernels/ccb_nvls.cuh"
 #include "../kernels/ccb_p2p.cuh"
+#include "../kernels/ccb_linkprobe.cuh"
 #include "../kernels/ccb_reduce.cuh"
 #include "../kernels/ccb_ring.cuh"
 #include "ccb/ccb.h"
@@ -670,6 +671,44 @@ extern "C" int ccb_all_reduce_symm(ccb_comm* c, uint64_t send_off, uint64_t recv
   const int cap = grid_cap(c, fn);
   return launch(c, fn, tiles < (size_t)cap ? (int)(tiles ? tiles : 1) : cap, &a, static_cast<cudaStream_t>(stream_));
 }
+// ---- link probe ---------------------------------------------------------------------------
+// Writes `bytes` from this rank into the data area of `peer`'s arena with the given store
+// method (see ccb_linkprobe.cuh). No collective may be in flight on the communicator; the
+// staging areas are overwritten. Time it with events on `stream`.
+extern "C" int ccb_link_probe(ccb_comm* c, int method, int peer, uint64_t bytes, ccb_stream_t stream_) {
+  int rc = check_alive(c);
+  if (rc) return rc;
+  if (method < 0 || method > 2 || peer < 0 || peer >= c->nranks || c->nlocal != 1) {
+    set_error("ccb_link_probe: method 0..2, a peer rank, one rank per process");
+    return CCB_ERR_ARG;
+  }
+  bytes &= ~(uint64_t)8191;
+  if (bytes == 0 || bytes > 2 * c->half_bytes) {
+    set_error("ccb_link_probe: %llu bytes do not fit the data area (%llu)", (unsigned long long)bytes, (unsigned long long)(2 * c->half_bytes));
+    return CCB_ERR_CAPACITY;
+  }
+  LinkProbeArgs a;
+  a.dst = c->arena[peer] + CCB_DATA_OFFSET;
+  a.bytes = bytes;
+  a.method = method;
+  const size_t smem = method == 0 ? 0 : (size_t)(kProbeThreads / 32) * kProbeStages * (method == 1 ? 512 : 2048);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaFuncSetAttribute(link_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (kProbeThreads / 32) * kProbeStages * 2048);
+    attr_set = true;
+  }
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+  link_probe_kernel<<<sms, kProbeThreads, smem, static_cast<cudaStream_t>(stream_)>>>(a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("link probe launch failed: %s", cudaGetErrorString(e));
+    return CCB_ERR_CUDA;
+  }
+  count_launch();
+  return CCB_OK;
+}
+
 // ---- point-to-point over the peer arenas --------------------------------------------------
 // ops: `nops` sends and receives of THIS rank, all launched as one kernel (what an
 // ncclGroupStart/End holds, or one call). Message sizes must match at the two ends.

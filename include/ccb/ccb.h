@@ -78,6 +78,13 @@ int ccb_comm_read_trace(ccb_comm* c, unsigned long long* out, int ctas);
 /* Wire bytes a call moves per rank for `count` elements (for ratio reporting). */
 uint64_t ccb_wire_bytes(int codec, int dtype, uint64_t count);
 
+/* ---- link probe ---------------------------------------------------------------------
+ * Writes `bytes` of generated data from this rank into the data area of `peer`'s arena and
+ * so measures what SM-issued stores reach on the link: method 0 = 16-byte stores per lane,
+ * 1 = bulk copies (TMA unit) of 512 bytes from shared memory, 2 = bulk copies of 2 KB. No
+ * collective may be in flight. Time it with events on `stream`. */
+int ccb_link_probe(ccb_comm* c, int method, int peer, uint64_t bytes, ccb_stream_t stream);
+
 /* ---- point-to-point ----------------------------------------------------------------
  * Sends and receives over the peer arenas, no NCCL involved: the sender stores into a
  * mailbox in the receiver's arena, the receiver copies out. ccb_p2p launches the
