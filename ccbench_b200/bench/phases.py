@@ -6,7 +6,12 @@ the marks are `globaltimer` reads by thread 0 of every CTA.
     python -m torch.distributed.run --nproc-per-node 4 -m ccbench_b200.bench.phases --what sz --field 384
 
 allreduce (two-shot): marks 0 start, 1 own lanes pushed to the owners, 3 own shard reduced,
-re-encoded and pushed to everybody, 4 all shards decoded. sz: 0 start, 1 own field packed
+re-encoded and pushed to everybody, 4 all shards decoded. Large messages run the
+warp-specialised pipelined kernel; its row gives mark 1 = first wave's lanes pushed (all
+warps), 2 = first wave reduced by the link warps, 3 = link warps done, 5 = first wave
+decoded, 4 = decode warps done, then the time the link leader waited for flags and the
+time the signal warp spent in fences; the row "plain" is the same call with the pipelined
+kernel switched off. sz: 0 start, 1 own field packed
 and copied out, 3 first received field decoded, 4 all decoded. Times are microseconds
 after the first CTA of the rank started, median / max over the CTAs.
 """
@@ -41,18 +46,21 @@ def _timed(fn, world, dev, iters=10):
     return t.item()
 
 
-def _trace(comm, fn, world, marks):
+def _trace(comm, fn, world, marks, extra=False):
     comm.set_trace(True)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     fn()
     torch.cuda.synchronize()
+    tr = comm.read_trace(1024).double()   # before tracing is switched off: that releases the marks
     comm.set_trace(False)
-    tr = comm.read_trace(1024).double()
     tr = tr[tr[:, 0] > 0]
     rel = (tr - tr[:, 0].min()) / 1e3
-    return f"ctas {tr.shape[0]} | " + " | ".join(f"mark {k}: {rel[:, k].median():.1f} / {rel[:, k].max():.1f}" for k in marks)
+    line = f"ctas {tr.shape[0]} | " + " | ".join(f"mark {k}: {rel[:, k].median():.1f} / {rel[:, k].max():.1f}" for k in marks)
+    if extra:
+        line += f" | waited {tr[:, 6].median() / 1e3:.1f} / {tr[:, 6].max() / 1e3:.1f} | in fences {tr[:, 7].median() / 1e3:.1f} / {tr[:, 7].max() / 1e3:.1f}"
+    return line
 
 
 def main(argv=None):
@@ -80,10 +88,19 @@ def main(argv=None):
                 for _ in range(5):
                     fn()
                 line = f"n={world} {nbytes >> 20} MiB {a.codec} {algo}: {_timed(fn, world, dev):.1f} us"
+                big = algo == "twoshot" and world > 1 and nbytes >= (64 << 20)
                 if algo == "twoshot":
-                    line += " | " + _trace(comm, fn, world, (1, 3, 4))
+                    line += " | " + (_trace(comm, fn, world, (1, 2, 3, 5, 4), extra=True) if big else _trace(comm, fn, world, (1, 3, 4)))
                 if rank == 0:
                     print(line, flush=True)
+                if big:
+                    comm.set_pipeline(0)
+                    for _ in range(3):
+                        fn()
+                    line = f"n={world} {nbytes >> 20} MiB {a.codec} twoshot plain: {_timed(fn, world, dev):.1f} us | " + _trace(comm, fn, world, (1, 3, 4))
+                    comm.set_pipeline(1)
+                    if rank == 0:
+                        print(line, flush=True)
             if world > 1:
                 z = x.clone()
                 for _ in range(5):

@@ -38,7 +38,8 @@ def timed(fn, iters, warmup, world, dev, flush=None):
         e.record()
         torch.cuda.synchronize()
         tot = s.elapsed_time(e)
-    else:  # small messages: flush L2 between iterations, time each call
+    else:  # small messages: flush L2 between iterations, time each call, report the median
+        each = []
         for _ in range(iters):
             flush.add_(1.0)
             if world > 1:
@@ -48,7 +49,8 @@ def timed(fn, iters, warmup, world, dev, flush=None):
             fn()
             e.record()
             torch.cuda.synchronize()
-            tot += s.elapsed_time(e)
+            each.append(s.elapsed_time(e))
+        tot = sorted(each)[len(each) // 2] * iters   # a single 300 us hiccup would swamp a 30 us mean
     t = torch.tensor([tot / iters], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

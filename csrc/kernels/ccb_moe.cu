@@ -41,7 +41,17 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
   T* dst = static_cast<T*>(a.dst[lr]);
   char* my = c.arena[r];
   const size_t area = CCB_DATA_OFFSET + (size_t)(c.epoch & 1u) * c.half_bytes;
-  const size_t H = a.hidden, upr = H / kWarpElems;  // units per row
+  const size_t H = a.hidden;
+  const unsigned int upr = (unsigned int)(H / kWarpElems);  // units per row (constant divisor above: a shift)
+  // unit -> (row, column) without a 64-bit division per unit: a shift when a row is a power
+  // of two of units (the usual hidden sizes), else a 32-bit division
+  const int upr_shift = (upr & (upr - 1u)) == 0 ? __ffs((int)upr) - 1 : -1;
+  auto row_of = [&](size_t u, size_t& col) -> size_t {
+    const unsigned int u32 = (unsigned int)u;
+    const unsigned int j = upr_shift >= 0 ? (u32 >> upr_shift) : (u32 / upr);
+    col = (size_t)(u32 - j * upr) * kWarpElems + (size_t)lane * kLaneElems;
+    return j;
+  };
   const size_t pad = a.slot_pad;
   if (threadIdx.x == 0) sync.fail = 0;
   __syncthreads();
@@ -51,7 +61,7 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
   // Destinations are visited starting with the next rank, (r + 1) % n, ..., r: at any moment
   // every rank stores to a different peer, so no inbound link takes all the traffic.
   for (int jd = 1; jd <= n; ++jd) {
-    const int p = (r + jd) % n;
+    const int p = r + jd < n ? r + jd : r + jd - n;
     const size_t rows = a.combine ? a.cnt[p][r] : a.cnt[r][p];
     size_t base_row = 0, send_row_off = 0;  // combine: first row of origin p; dispatch: offset into perm
     for (int s = 0; s < p; ++s) {
@@ -63,7 +73,8 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
     for (size_t t = b; t * kWarps < units; t += G) {
       const size_t u = t * kWarps + warp;
       if (u >= units) continue;
-      const size_t j = u / upr, col = (u % upr) * kWarpElems + (size_t)lane * kLaneElems;
+      size_t col;
+      const size_t j = row_of(u, col);
       const size_t srow = a.combine ? base_row + j : (size_t)a.perm[lr][send_row_off + j];
       float v[16];
       load16<T>(src + srow * H, col, H, v);
@@ -91,7 +102,8 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
       for (size_t t = b; t * kWarps < units; t += G) {
         const size_t u = t * kWarps + warp;
         if (u >= units) continue;
-        const size_t j = u / upr, col = (u % upr) * kWarpElems + (size_t)lane * kLaneElems;
+        size_t col;
+        const size_t j = row_of(u, col);
         typename C::Packet pk;
         C::load(slot, pad, j * H + col, pk);
         float d[16];
@@ -116,7 +128,8 @@ __global__ void __launch_bounds__(kThreads, 2) moe_kernel(const __grid_constant_
   for (size_t t = b; t * kWarps < units; t += G) {
     const size_t u = t * kWarps + warp;
     if (u >= units) continue;
-    const size_t tok = u / upr, col = (u % upr) * kWarpElems + (size_t)lane * kLaneElems;
+    size_t col;
+    const size_t tok = row_of(u, col);
     float acc[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[i] = 0.f;
@@ -177,6 +190,10 @@ static int moe_launch(ccb_comm* c, MoeArgs& a, int dtype, int codec, uint64_t ma
   a.rank0 = ccb_comm_rank(c);
   a.nlocal = ccb_comm_nlocal(c);
   const size_t units = (size_t)work_rows * (a.hidden / kWarpElems);
+  if (units >> 32 || ((uint64_t)max_rows * (a.hidden / kWarpElems)) >> 32) {  // the kernel indexes units with 32 bits
+    set_error("MoE block too large: %llu rows of %llu elements", (unsigned long long)work_rows, (unsigned long long)a.hidden);
+    return CCB_ERR_CAPACITY;
+  }
   size_t tiles = (units + kWarps - 1) / kWarps;
   int cap = grid_cap(c, fn);
   if (tiles < 1) tiles = 1;

@@ -84,6 +84,12 @@ struct SzArgs {
   int rank0, nlocal;
   unsigned int bcast_waves;          // progress steps a broadcast root publishes (1..kMaxBcastWaves)
   unsigned long long slot_bytes;     // arena bytes of one source's slot (ngroups * kGroupStride, rounded)
+  // Division of a tile index by tiles_x and by tiles_x * tiles_y as a multiplication:
+  // magic = floor(2^40 / d) + 1 and q = (tile * magic) >> 40, exact for tile < 2^22 and
+  // d < 2^18 (then tile * d < 2^40 and the product fits 64 bits; the host checks the two
+  // limits, 0 = use the division). An integer division by a run-time value
+  // costs about 25 instructions, and every thread needs three per tile.
+  unsigned long long magic_x, magic_xy;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -116,7 +122,16 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 struct TileCoord { int x0, y0, z0; };
 __device__ __forceinline__ TileCoord tile_coord(const SzArgs& a, unsigned int tile) {
   TileCoord t;
-  const unsigned int tx = tile % a.tiles_x, ty = (tile / a.tiles_x) % a.tiles_y, tz = tile / (a.tiles_x * a.tiles_y);
+  unsigned int tx, ty, tz;
+  if (a.magic_x) {
+    const unsigned int txy = a.tiles_x * a.tiles_y;
+    tz = (unsigned int)(((unsigned long long)tile * a.magic_xy) >> 40);
+    const unsigned int rem = tile - tz * txy;
+    ty = (unsigned int)(((unsigned long long)rem * a.magic_x) >> 40);
+    tx = rem - ty * a.tiles_x;
+  } else {
+    tx = tile % a.tiles_x, ty = (tile / a.tiles_x) % a.tiles_y, tz = tile / (a.tiles_x * a.tiles_y);
+  }
   t.x0 = tx * kTX; t.y0 = ty * kTY; t.z0 = tz * kTZ;
   return t;
 }
@@ -623,6 +638,15 @@ static void fill_geometry(SzArgs& a, int nx, int ny, int nz, float eb) {
   a.tiles_z = (nz + kTZ - 1) / kTZ;
   const unsigned long long tiles = (unsigned long long)a.tiles_x * a.tiles_y * a.tiles_z;
   a.ngroups = (unsigned int)((tiles + kClusterSize - 1) / kClusterSize);
+  const unsigned long long txy = (unsigned long long)a.tiles_x * a.tiles_y;
+  // tile indices run up to ngroups * kClusterSize (the last group may be partly empty)
+  const unsigned long long max_tile = (unsigned long long)a.ngroups * kClusterSize;
+  if (max_tile < (1ull << 22) && txy < (1ull << 18)) {
+    a.magic_x = (1ull << 40) / (unsigned long long)a.tiles_x + 1;
+    a.magic_xy = (1ull << 40) / txy + 1;
+  } else {
+    a.magic_x = a.magic_xy = 0;
+  }
   a.eb = eb;
   a.two_eb = 2.f * eb * (1.f - 0.0009765625f);  // quantisation step: 2 eb (1 - 2^-10)
   a.inv_two_eb = 1.f / a.two_eb;

@@ -1023,9 +1023,11 @@ extern "C" int ccb_all_reduce(ccb_comm* c, const void* const* send, void* const*
     // It wins while the extra (n-1)(1-2/n) * S bytes cost less than that latency at the
     // ~600 GB/s an SM-driven NVLink stream sustains, i.e. below about
     // 6 MB / ((n-1)(1-2/n)) of wire bytes; with two ranks both shapes move the same
-    // bytes and one-shot stays ahead until its n-way local reduction dominates (32 MiB).
+    // bytes and one-shot stays ahead until the pipelined two-shot kernel overtakes it
+    // (measured: int8 95 against 110 us at 35 MB of wire, 351 against 265 us at 138 MB;
+    // uncompressed 62 against 76 us at 17 MB, 146 against 140 us at 67 MB): 48 MiB.
     const size_t wire = codec_slot_bytes(codec, dtype, round_up(count, kWarpElems));
-    size_t limit = n <= 2 ? ((size_t)32 << 20) : (size_t)(6.0e6 / ((n - 1) * (1.0 - 2.0 / n)));
+    size_t limit = n <= 2 ? ((size_t)48 << 20) : (size_t)(6.0e6 / ((n - 1) * (1.0 - 2.0 / n)));
     limit = (size_t)env_u64("CCB_ONESHOT_MAX_BYTES", limit);
     const bool fits = (size_t)n * wire <= c->half_bytes;
     algo = (n > 1 && fits && wire <= limit) ? CCB_ALGO_ONESHOT : CCB_ALGO_TWOSHOT;
