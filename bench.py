@@ -77,9 +77,37 @@ def main():
     from ccbench_b200.utils.numa import bind_to_gpu_node
     numa = bind_to_gpu_node(local_rank)
     dev = torch.device("cuda", local_rank)
+    pipelined = "on"
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # Pre-flight of the warp-specialised kernel on a scratch communicator with a short
+        # limit on its device-side waits: if it does not complete or does not add up on this
+        # job shape, the timed communicator runs the plain two-shot kernel instead. A wait
+        # that runs out returns an error status; nothing hangs.
+        scratch = Communicator.from_torch_distributed(arena_bytes=256 << 20)
+        scratch.set_timeout_ms(3000)
+        scratch.set_pipeline(2)
+        px = gradient_like(32 << 20, torch.bfloat16, seed=100 + rank, device=dev)   # 64 MiB: several waves per CTA
+        py = torch.empty_like(px)
+        want = px.float().clone()
+        dist.all_reduce(want)
+        ok = 1
+        try:
+            scratch.all_reduce(px, py, codec="int8", algo="twoshot")
+            torch.cuda.synchronize()
+            rel = ((py.float() - want).norm() / want.norm()).item()
+            if scratch.status()[0] != 0 or not rel < 0.1:
+                ok = 0
+        except Exception:
+            ok = 0
+        flag = torch.tensor([ok], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        scratch.close()
+        del px, py, want
         comm = Communicator.from_torch_distributed(nvls=(args.algo == "nvls"))
+        if int(flag.item()) == 0:
+            comm.set_pipeline(0)
+            pipelined = "off: its pre-flight on a scratch communicator failed"
     else:
         comm = Communicator.create(0, 1, f"bench{os.getpid()}")
 
@@ -254,7 +282,7 @@ def main():
                        "message_bytes_per_rank": args.bytes, "codec": args.codec, "algo": args.algo,
                        "algo_selection": ("measured before warm-up; ring (n requantisations) only if > 15 % faster than "
                                           "two-shot (2 requantisations)") if requested == "tune" else "fixed",
-                       "algo_candidates": tuning,
+                       "algo_candidates": tuning, "pipelined_kernel": pipelined,
                        "error_feedback": bool(args.error_feedback),
                        "parallelism": f"dp{world}", "l2": "inputs (256 MiB) larger than L2, no flush needed",
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},
