@@ -180,3 +180,30 @@ def test_large_message_takes_the_pipelined_kernel_by_default(comms):
     rel = ((out[0].float() - exact).norm() / exact.norm()).item()
     assert rel < 0.03
     assert torch.equal(out[0], out[1])
+
+
+def test_link_probe_methods_run_and_reject_bad_arguments():
+    """The store-method probe on a one-rank communicator (the "peer" is the own arena): vector
+    stores and both bulk-copy sizes complete, sizes beyond the data area and unknown methods
+    are refused before anything is launched."""
+    import ctypes
+    import os
+
+    from ccbench_b200._lib import lib
+    from ccbench_b200.comm import CcbError, _check
+
+    comm = Communicator.create(0, 1, f"probe{os.getpid()}", arena_bytes=128 << 20)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        for method in (0, 1, 2):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _check(lib().ccb_link_probe(comm._h, method, 0, 32 << 20, stream))
+            e1.record()
+            torch.cuda.synchronize()
+            assert e0.elapsed_time(e1) > 0 and comm.status()[0] == 0
+        for bad in ((3, 0, 1 << 20), (0, 1, 1 << 20), (0, 0, 1 << 40)):
+            with pytest.raises(CcbError):
+                _check(lib().ccb_link_probe(comm._h, bad[0], bad[1], ctypes.c_uint64(bad[2]), stream))
+    finally:
+        comm.close()
