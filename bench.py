@@ -44,6 +44,7 @@ def parse():
                          "requantisation per hop) is kept only when it is more than 15 %% faster")
     ap.add_argument("--error-feedback", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-call-overlap", action="store_true", help="time the calls strictly one after the other")
     ap.add_argument("--via", default="api", choices=["api", "interposer"],
                     help="interposer: also run the same collective through the NCCL benchmark driver under "
                          "LD_PRELOAD=libccb_nccl.so and report its device time beside the direct-API time")
@@ -102,19 +103,43 @@ def main():
             ok = 0
         flag = torch.tensor([ok], device=dev)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        # the same for consecutive calls that overlap tail and head (alternating outputs)
+        ok2 = int(flag.item())
+        if ok2:
+            try:
+                py2 = torch.empty_like(px)
+                scratch.set_call_overlap(True)
+                for k in range(6):
+                    scratch.all_reduce(px, (py, py2)[k & 1], codec="int8", algo="twoshot")
+                torch.cuda.synchronize()
+                for out in (py, py2):
+                    rel = ((out.float() - want).norm() / want.norm()).item()
+                    if scratch.status()[0] != 0 or not rel < 0.1:
+                        ok2 = 0
+                del py2
+            except Exception:
+                ok2 = 0
+        flag2 = torch.tensor([ok2], device=dev)
+        dist.all_reduce(flag2, op=dist.ReduceOp.MIN)
         scratch.close()
         del px, py, want
         comm = Communicator.from_torch_distributed(nvls=(args.algo == "nvls"))
         if int(flag.item()) == 0:
             comm.set_pipeline(0)
             pipelined = "off: its pre-flight on a scratch communicator failed"
+        overlap_ok = int(flag2.item()) == 1 and not args.error_feedback and not args.no_call_overlap
     else:
         comm = Communicator.create(0, 1, f"bench{os.getpid()}")
+        overlap_ok = False
 
     dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[args.dtype]
     count = args.bytes // torch.empty((), dtype=dtype).element_size()
     x = gradient_like(count, dtype, seed=rank, device=dev)
     y = torch.empty_like(x)
+    # Consecutive timed calls write alternating output buffers (as the buckets of a gradient
+    # synchronisation do), which lets call k + 1 start on the SMs that call k's CTAs have left.
+    ys = [y, torch.empty_like(x)] if overlap_ok else [y]
+    ncalls = [0]
     ef = torch.zeros(count, device=dev) if args.error_feedback else None
 
     def barrier():
@@ -136,7 +161,21 @@ def main():
             args.algo = "twoshot"
 
     def step():
-        comm.all_reduce(x, y, codec=args.codec, algo=args.algo, error_feedback=ef)
+        comm.all_reduce(x, ys[ncalls[0] % len(ys)], codec=args.codec, algo=args.algo, error_feedback=ef)
+        ncalls[0] += 1
+
+    def timed_loop():
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        a.record()
+        for _ in range(args.steps):
+            step()
+        b.record()
+        barrier()
+        tt = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return tt.item() / args.steps
 
     # Warm up for at least W steps AND about a second, so that the clock sampler (one
     # nvidia-smi sample per 100 ms) sees the GPU under the same load as the timed steps.
@@ -164,6 +203,17 @@ def main():
     if rc != 0:
         raise SystemExit(f"communicator error during warm-up: {words}")
 
+    # ---- the same K steps with every call waiting for the whole call before it ----
+    serialised_ms = None
+    if overlap_ok and args.algo == "twoshot":
+        serialised_ms = timed_loop()
+        comm.set_call_overlap(True)
+        for _ in range(4):
+            step()
+    call_overlap = ("on: consecutive calls write alternating output buffers and the first CTAs of call k+1 start on the SMs "
+                    "that call k's CTAs have left (Communicator.set_call_overlap); serialised_ms_per_step is the same loop "
+                    "without it") if serialised_ms is not None else "off"
+
     # ---- device-timed region -------------------------------------------------
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     l0 = launch_count()
@@ -176,6 +226,9 @@ def main():
     sampler.__exit__(None, None, None)
     clk = sampler
     launches = launch_count() - l0
+    rc, words = comm.status()
+    if rc != 0:
+        raise SystemExit(f"communicator error in the timed region: {words}")
     ms = start.elapsed_time(stop)
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
@@ -187,8 +240,11 @@ def main():
     exact = x.float().clone()
     if world > 1:
         dist.all_reduce(exact)
-    rel_l2 = ((y.float() - exact).norm() / exact.norm()).item()
+    comm.set_call_overlap(False)
+    rel_l2 = max(((out.float() - exact).norm() / exact.norm()).item() for out in ys)
     del exact
+    if len(ys) > 1:
+        ys.pop()
 
     # ---- end to end: pinned host input -> H2D -> AllReduce -> D2H of a sample ----
     e2e = None
@@ -282,13 +338,13 @@ def main():
                        "message_bytes_per_rank": args.bytes, "codec": args.codec, "algo": args.algo,
                        "algo_selection": ("measured before warm-up; ring (n requantisations) only if > 15 % faster than "
                                           "two-shot (2 requantisations)") if requested == "tune" else "fixed",
-                       "algo_candidates": tuning, "pipelined_kernel": pipelined,
+                       "algo_candidates": tuning, "pipelined_kernel": pipelined, "call_overlap": call_overlap,
                        "error_feedback": bool(args.error_feedback),
                        "parallelism": f"dp{world}", "l2": "inputs (256 MiB) larger than L2, no flush needed",
                        "busbw_formula": "bytes/t*2(n-1)/n; n=1 reports algbw"},
             "algbw": algbw, "ref_definition_bw": 2 * algbw, "compression_ratio": wire_ratio(args.codec, dtype),
             "rel_l2_error": rel_l2, "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
-            "e2e": e2e, "via_interposer": interposed, "gpu_launches": launches, "host_numa_binding": numa, "roofline": roofline,
+            "serialised_ms_per_step": serialised_ms, "e2e": e2e, "via_interposer": interposed, "gpu_launches": launches, "host_numa_binding": numa, "roofline": roofline,
         }
         print(json.dumps(line), flush=True)
     comm.close()

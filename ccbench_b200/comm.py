@@ -111,6 +111,14 @@ class Communicator:
         L.ccb_comm_set_noncooperative.argtypes = [ctypes.c_void_p, ctypes.c_int]
         _check(L.ccb_comm_set_noncooperative(self._h, ctas))
 
+    def set_call_overlap(self, on: bool) -> None:
+        """Let consecutive large all_reduce / reduce_scatter calls on one stream overlap tail and
+        head (the first CTAs of the next call start on the SMs the previous call's CTAs have
+        left). Promise: consecutive calls use different tensors (buckets, double buffers)."""
+        L = lib()
+        L.ccb_comm_set_call_overlap.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        _check(L.ccb_comm_set_call_overlap(self._h, 1 if on else 0))
+
     def set_waves(self, waves: int) -> None:
         L = lib()
         L.ccb_comm_set_waves.argtypes = [ctypes.c_void_p, ctypes.c_int]

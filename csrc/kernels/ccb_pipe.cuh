@@ -203,6 +203,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
     for (int w = 0; w <= W; ++w) sh.kb[s][w] = (unsigned int)((unsigned long long)K * (unsigned)w / (unsigned)W);
   }
   __syncthreads();  // the only CTA-wide barrier: the roles part ways here
+  // The next call of the stream may start on the SMs that this grid's CTAs leave (when it was
+  // launched with the programmatic-serialisation attribute; a no-op otherwise). Nothing here
+  // waits for the grid before this one: see the launch in the runtime.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   auto wave_items = [&](int s, int w, unsigned int& kb) -> unsigned int {
     kb = sh.kb[s][w];

@@ -136,6 +136,7 @@ struct ccb_comm {
   int rank0 = 0, nlocal = 1, nranks = 1, device = 0;
   size_t arena_bytes = 0;   // per rank, mapped size
   size_t half_bytes = 0;
+  int call_overlap = 0;     // consecutive pipelined calls may overlap tail and head (caller's promise: disjoint buffers)
   size_t symm_top = 0;      // symmetric allocations grow down from here
   size_t symm_limit = 0;    // top of the allocatable part (below the point-to-point mailboxes)
   size_t p2p_offset = 0;    // mailboxes of ccb_p2p: [source][lane][half][p2p_lane_bytes]; 0 = none
@@ -250,9 +251,35 @@ int grid_cap(ccb_comm* c, const void* kernel, int threads) {
   return cap < 1 ? 1 : cap;
 }
 
-int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream, int threads) {
+int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream, int threads, bool may_overlap) {
   dim3 grid((unsigned)ctas, (unsigned)c->nlocal, 1), block((unsigned)threads, 1, 1);
   void* params[] = {args};
+  // Consecutive calls may overlap tail and head (ccb_comm_set_call_overlap): the launch is
+  // plain and carries the programmatic-serialisation attribute, so its CTAs start on the SMs
+  // that the CTAs of the call before leave, instead of after the slowest of them. The kernel
+  // says "dependents may launch" at its start and never waits for the grid before it: the
+  // caller has promised that consecutive calls touch different user buffers, and the staging
+  // halves and flags alternate by epoch. One CTA of 1024 threads fills an SM, so the call
+  // after the next cannot start before this one has left the device.
+  if (may_overlap && c->call_overlap && c->nlocal == 1) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelExC(&cfg, kernel, params);
+    if (e != cudaSuccess) {
+      set_error("kernel launch failed: %s", cudaGetErrorString(e));
+      return CCB_ERR_CUDA;
+    }
+    count_launch();
+    return CCB_OK;
+  }
   // A cooperative launch starts only when the WHOLE grid fits beside what is running, so
   // behind a stream of GEMMs it waits for a full wave to drain. With one rank per launch
   // no CTA waits on another CTA of its own grid (only on the same-numbered CTA of the
@@ -779,6 +806,11 @@ extern "C" int ccb_recv(ccb_comm* c, void* buf, uint64_t bytes, int peer, ccb_st
   ccb_p2p_op o = {buf, bytes, peer, 1};
   return ccb_p2p(c, &o, 1, stream);
 }
+extern "C" int ccb_comm_set_call_overlap(ccb_comm* c, int on) {
+  if (!c) return CCB_ERR_ARG;
+  c->call_overlap = on ? 1 : 0;
+  return CCB_OK;
+}
 extern "C" int ccb_comm_set_noncooperative(ccb_comm* c, int ctas) {
   if (!c || ctas < 0) return CCB_ERR_ARG;
   c->noncoop_ctas = ctas;
@@ -940,7 +972,7 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
     a.tile_warps = kWarps;
     a.link_warps = c->pipe_link_warps;
     a.use_mc = (c->mc_arena && c->nlocal == 1 && c->pipe_mc) ? 1 : 0;
-    return launch(c, fn, pipe_ctas, &a, stream, pipe_kernel_threads());
+    return launch(c, fn, pipe_ctas, &a, stream, pipe_kernel_threads(), true);
   }
   const int ctas = ctas_for(c, fn, shard_elems < count ? shard_elems : count, &a.tile_warps);
   // Each extra wave of the non-specialised kernel costs a pipeline drain (fence + flag

@@ -12,7 +12,7 @@ void count_launch();
 CommDev comm_dev(ccb_comm* c, uint32_t epoch);
 uint32_t next_epoch(ccb_comm* c);
 int grid_cap(ccb_comm* c, const void* kernel, int threads = 512);
-int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream, int threads = 512);
+int launch(ccb_comm* c, const void* kernel, int ctas, void* args, cudaStream_t stream, int threads = 512, bool may_overlap = false);
 int check_alive(ccb_comm* c);
 size_t elem_size(int dtype);
 size_t codec_slot_bytes(int codec, int dtype, size_t pad);

@@ -56,6 +56,13 @@ int ccb_comm_set_max_ctas(ccb_comm* c, int ctas);
  * stream: a plain launch trickles into SMs as they free up instead of waiting for room
  * for the whole grid. One rank per process only; every wait stays bounded. */
 int ccb_comm_set_noncooperative(ccb_comm* c, int ctas);
+/* on != 0: consecutive large AllReduce / ReduceScatter calls of this communicator on one stream
+ * may overlap: the first CTAs of call k + 1 start on the SMs that the CTAs of call k have left,
+ * instead of after its slowest CTA (programmatic dependent launch; one rank per process). The
+ * caller promises that call k + 1 neither reads what call k writes nor writes what it reads or
+ * writes (gradient buckets, double-buffered outputs). Any other kernel put on the stream
+ * afterwards is ordered after all of them as usual. Off by default. */
+int ccb_comm_set_call_overlap(ccb_comm* c, int on);
 /* Software-pipeline depth of the two-shot kernels (0 = choose per call, at most 8). */
 int ccb_comm_set_waves(ccb_comm* c, int waves);
 /* The warp-specialised pipelined two-shot kernel (large AllReduce / ReduceScatter):

@@ -119,6 +119,7 @@ def _body(comm, rank, world, dev):
     _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs)
     _sz_and_moe(comm, rank, world, dev, gather_inputs)
     _point_to_point(comm, rank, world, dev)
+    _overlapping_calls(comm, rank, world, dev, gather_inputs)
 
 
 def _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs):
@@ -201,6 +202,35 @@ def _pipelined_and_plain_launches(comm, rank, world, dev, gather_inputs):
     comm.set_max_ctas(0)
     comm.set_noncooperative(0)
     assert comm.status()[0] == 0
+
+
+def _overlapping_calls(comm, rank, world, dev, gather_inputs):
+    """Consecutive pipelined calls that may overlap tail and head: different inputs and
+    alternating outputs, every result equal to what the same call gives alone, and a kernel
+    put on the stream afterwards sees all of them."""
+    count = (1 << 22) + 4097
+    xs = [(torch.randn(count, generator=torch.Generator(device=dev).manual_seed(300 + 7 * k + rank), device=dev) * (k + 1)).to(torch.bfloat16)
+          for k in range(3)]
+    alone = []
+    comm.set_pipeline(2)
+    for x in xs:
+        y = torch.empty_like(x)
+        comm.all_reduce(x, y, codec="int8", algo="twoshot")
+        alone.append(y)
+    torch.cuda.synchronize()
+    comm.set_call_overlap(True)
+    outs = [torch.zeros_like(x) for x in xs]
+    for rep in range(3):
+        for k in range(3):
+            comm.all_reduce(xs[k], outs[k], codec="int8", algo="twoshot")
+    total = sum(o.float().sum() for o in outs)          # ordinary kernels, ordered after every call
+    torch.cuda.synchronize()
+    comm.set_call_overlap(False)
+    comm.set_pipeline(1)
+    assert comm.status()[0] == 0, comm.status()
+    for k in range(3):
+        assert torch.equal(outs[k], alone[k]), ("overlapping calls", k)
+    assert torch.isfinite(total)
 
 
 def _point_to_point(comm, rank, world, dev):
