@@ -131,6 +131,7 @@ def main():
     else:
         comm = Communicator.create(0, 1, f"bench{os.getpid()}")
         overlap_ok = False
+        pipelined = "not used with one rank"
 
     dtype = {"bf16": torch.bfloat16, "f32": torch.float32, "f16": torch.float16}[args.dtype]
     count = args.bytes // torch.empty((), dtype=dtype).element_size()
