@@ -171,6 +171,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int L = a.link_warps, D = kPipeWarps - 1 - L;  // the last warp signals
   const int W = a.waves;
+  // Two calls of this rank may be on the device at once when calls overlap (a late CTA of call
+  // k beside an early CTA of call k + 1 with the same index): they use different flag rows, or
+  // the late one could put an older epoch over a newer one in a peer's flag word.
+  const int rb = a.row_base;
   const bool ar = (a.mode == CCB_MODE_ALLREDUCE);
   const T* send = static_cast<const T*>(a.send[lr]);
   T* recv = static_cast<T*>(a.recv[lr]);
@@ -376,7 +380,7 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
           warp_arrive(&sh.p1_done[w + 1]);
         }
         const uint64_t tw0 = tr ? globaltimer_ns() : 0;
-        if (!group_wait(leader, &sh.p1_ready, w, 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
+        if (!group_wait(leader, &sh.p1_ready, w, rb + 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
         if (tr) waited += globaltimer_ns() - tw0;
         phase2(w, warp, L);
         warp_arrive(&sh.p2_done[w]);
@@ -404,10 +408,10 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
     }
     for (int w = 0; w < W; ++w) {
       if (ar) {
-        if (!group_wait(leader, &sh.p2_ready, w, 2 * w + 1, c, my, r, sh, 0x20 | (w << 16))) return;
+        if (!group_wait(leader, &sh.p2_ready, w, rb + 2 * w + 1, c, my, r, sh, 0x20 | (w << 16))) return;
         if (w + 1 < W) phase3(w, gw, D); else phase3(w, warp, kData);
       } else {
-        if (!group_wait(leader, &sh.p1_ready, w, 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
+        if (!group_wait(leader, &sh.p1_ready, w, rb + 2 * w, c, my, r, sh, 0x10 | (w << 16))) return;
         phase2(w, gw, D);
       }
       if (leader && w == 0) mark(5);
@@ -426,15 +430,15 @@ __global__ void __launch_bounds__(kPipeThreads, 1) pipe_kernel(const __grid_cons
       if (tr) fenced += globaltimer_ns() - t0;
     };
     if (!warp_wait_counter(&sh.p1_done[0], first, sh, c, my, 0xA0)) return;
-    publish(0);
+    publish(rb);
     for (int w = 0; w < W; ++w) {
       if (w + 1 < W) {
         if (!warp_wait_counter(&sh.p1_done[w + 1], (unsigned)L, sh, c, my, 0xA0 | ((w + 1) << 16))) return;
-        publish(2 * (w + 1));
+        publish(rb + 2 * (w + 1));
       }
       if (ar) {
         if (!warp_wait_counter(&sh.p2_done[w], (unsigned)L, sh, c, my, 0xB0 | (w << 16))) return;
-        publish(2 * w + 1);
+        publish(rb + 2 * w + 1);
       }
     }
     if (tr) c.trace[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * CCB_TRACE_SLOTS + 7] = fenced;

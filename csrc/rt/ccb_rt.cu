@@ -943,6 +943,8 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
       const int most = c->waves > 0 ? CCB_MAX_SLOTS / 2 : (c->nranks <= 2 ? 6 : CCB_MAX_SLOTS / 2);
       if (w > most) w = most;
       if (w > CCB_MAX_SLOTS / 2) w = CCB_MAX_SLOTS / 2;
+      // overlapping calls alternate between the two halves of the flag rows: 4 waves each
+      if (c->call_overlap && c->nlocal == 1 && w > CCB_MAX_SLOTS / 4) w = CCB_MAX_SLOTS / 4;
       if (w < 1) w = 1;
       pipe_waves = w;
       pipe_ctas = (int)(ctas ? ctas : 1);
@@ -971,6 +973,7 @@ static int reduce_launch(ccb_comm* c, const void* const* send, void* const* recv
     a.waves = pipe_waves;
     a.tile_warps = kWarps;
     a.link_warps = c->pipe_link_warps;
+    a.row_base = (c->call_overlap && c->nlocal == 1 && (a.c.epoch & 1u)) ? CCB_MAX_SLOTS / 2 : 0;
     a.use_mc = (c->mc_arena && c->nlocal == 1 && c->pipe_mc) ? 1 : 0;
     return launch(c, fn, pipe_ctas, &a, stream, pipe_kernel_threads(), true);
   }

@@ -85,6 +85,7 @@ typedef struct ReduceArgs {
   int op, root, mode;
   int waves;                  /* software-pipeline depth of the two-shot shape  */
   int tile_warps;             /* warps of a CTA that carry data: tile = 512 * tile_warps */
+  int row_base;               /* pipelined two-shot: first flag row of this call (0, or 8 for odd epochs when calls may overlap) */
   int link_warps;             /* pipelined two-shot: warps that store over NVLink (the rest decode, one signals) */
   int use_mc;                 /* pipelined two-shot: phase 2 stores once to the NVLS multicast address */
 } ReduceArgs;
