@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 2) nvls_inplace_kernel(const __grid_
   if (threadIdx.x == 0) sync.fail = 0;
   __syncthreads();
   const uint32_t peers = ((1u << n) - 1u) & ~(1u << r);
-  // round 1: what earlier kernels of this stream wrote into the input is visible everywhere
+  // first flag exchange: what earlier kernels of this stream wrote into the input is visible everywhere
   if (threadIdx.x == 0) signal_peers(c, peers, 0, r, b);
   if (!cta_wait_sources(sync, c, my, 0, r, 0xffu, 0x88)) return;
   const char* mc_in = c.mc_arena + send_off;
