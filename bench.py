@@ -228,13 +228,33 @@ def main():
     clk = sampler
     launches = launch_count() - l0
     rc, words = comm.status()
-    if rc != 0:
-        raise SystemExit(f"communicator error in the timed region: {words}")
+    failed = torch.tensor([1 if rc != 0 else 0], device=dev)
+    if world > 1:
+        dist.all_reduce(failed, op=dist.ReduceOp.MAX)
     ms = start.elapsed_time(stop)
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_per_step = t.item() / args.steps
+    if int(failed.item()):
+        if serialised_ms is None:
+            raise SystemExit(f"communicator error in the timed region: {words}")
+        # The loop of overlapping calls did not complete on some rank (a device-side wait gave
+        # up; nothing hangs). The serialised loop of the same K steps, timed just before, is
+        # the measurement; the rest of the run uses a fresh communicator without overlap.
+        ms_per_step = serialised_ms
+        call_overlap = f"off: the loop of overlapping calls did not complete (status {words}); the value is the serialised loop"
+        try:
+            comm.close()
+        except Exception:
+            pass
+        comm = Communicator.from_torch_distributed(nvls=(args.algo == "nvls"))
+        if pipelined != "on":
+            comm.set_pipeline(0)
+        ys = [y]
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
     clocks = clk.summary()
 
     # ---- accuracy of the last result against the exact fp32 sum ----------------

@@ -217,12 +217,17 @@ __device__ __forceinline__ uint32_t pack_tile(float* vals, unsigned char* pk, in
     bad |= !(fabsf(s) < kQMax);  // also catches NaN / Inf
     float rf = __fadd_rn(__fadd_rn(s, kRoundMagic), -kRoundMagic);
     const float diff = __fsub_rn(x[e], __fmul_rn(rf, a.two_eb));  // against the decoder's own product (no FMA)
-    rf += diff > half ? 1.f : 0.f;                                // fp32 rounding picked the farther grid point
-    rf -= -diff > half ? 1.f : 0.f;
-    // The grid step is a shade under 2 eb, which absorbs the rounding of q * step for
-    // |q| < 2^13. Beyond that a value can fall between two grid points that are both more
-    // than eb away: such a tile is stored raw, so the bound always holds.
-    bad |= fabsf(__fsub_rn(x[e], __fmul_rn(rf, a.two_eb))) > a.eb;
+    // Nearly always |diff| <= step / 2 < eb: the value sits on the nearest grid point and the
+    // bound holds, nothing to correct or to re-check. The correction runs only when some lane
+    // of the warp needs it (NaN counts as needing it), with the same result either way.
+    if (__any_sync(0xffffffffu, !(fabsf(diff) <= half))) {
+      rf += diff > half ? 1.f : 0.f;                              // fp32 rounding picked the farther grid point
+      rf -= -diff > half ? 1.f : 0.f;
+      // The grid step is a shade under 2 eb, which absorbs the rounding of q * step for
+      // |q| < 2^13. Beyond that a value can fall between two grid points that are both more
+      // than eb away: such a tile is stored raw, so the bound always holds.
+      bad |= fabsf(__fsub_rn(x[e], __fmul_rn(rf, a.two_eb))) > a.eb;
+    }
     q[e] = (int)rf;
   }
   const bool raw_tile = __syncthreads_or(bad);
