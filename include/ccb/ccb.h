@@ -61,7 +61,9 @@ int ccb_comm_set_noncooperative(ccb_comm* c, int ctas);
  * instead of after its slowest CTA (programmatic dependent launch; one rank per process). The
  * caller promises that call k + 1 neither reads what call k writes nor writes what it reads or
  * writes (gradient buckets, double-buffered outputs). Any other kernel put on the stream
- * afterwards is ordered after all of them as usual. Off by default. */
+ * afterwards is ordered after all of them as usual. In this mode a call uses at most 4 waves
+ * (the two calls that can be on the device at once take one half of the flag rows each).
+ * Off by default. */
 int ccb_comm_set_call_overlap(ccb_comm* c, int on);
 /* Software-pipeline depth of the two-shot kernels (0 = choose per call, at most 8). */
 int ccb_comm_set_waves(ccb_comm* c, int waves);
