@@ -272,14 +272,21 @@ def main():
     if not args.no_e2e:
         hx = torch.empty(count, dtype=dtype).pin_memory()
         hx.copy_(x)
-        hy = torch.empty(count, dtype=dtype).pin_memory()   # the whole result comes back every step
-        copy_stream = torch.cuda.Stream()
+        # the whole result comes back every step, into two pinned buffers in turn
+        hy = [torch.empty(count, dtype=dtype).pin_memory(), torch.empty(count, dtype=dtype).pin_memory()]
+        copy_stream, back_stream = torch.cuda.Stream(), torch.cuda.Stream()
         xin = [torch.empty_like(x), torch.empty_like(x)]
+        yout = [y, torch.empty_like(x)]
         ready = [torch.cuda.Event(), torch.cuda.Event()]
         freed = [torch.cuda.Event(), torch.cuda.Event()]
+        done = [torch.cuda.Event(), torch.cuda.Event()]
+        copied = [torch.cuda.Event(), torch.cuda.Event()]
 
         def e2e_loop(k):
-            # step i's input upload overlaps step i-1's collective (two device buffers)
+            # Three stages in flight: the upload of step i+1, the collective of step i and the
+            # read-back of step i-1 (two device buffers each way). The host waits for the
+            # result of step i-1 while step i runs, and for the last one at the end.
+            main = torch.cuda.current_stream()
             with torch.cuda.stream(copy_stream):
                 xin[0].copy_(hx, non_blocking=True)
                 ready[0].record()
@@ -291,11 +298,20 @@ def main():
                             copy_stream.wait_event(freed[nxt])
                         xin[nxt].copy_(hx, non_blocking=True)
                         ready[nxt].record()
-                torch.cuda.current_stream().wait_event(ready[cur])
-                comm.all_reduce(xin[cur], y, codec=args.codec, algo=args.algo, error_feedback=ef)
+                main.wait_event(ready[cur])
+                if i >= 2:
+                    main.wait_event(copied[cur])          # the output buffer has been read back
+                comm.all_reduce(xin[cur], yout[cur], codec=args.codec, algo=args.algo, error_feedback=ef)
                 freed[cur].record()
-                hy.copy_(y, non_blocking=True)
-                torch.cuda.current_stream().synchronize()
+                done[cur].record()
+                with torch.cuda.stream(back_stream):
+                    back_stream.wait_event(done[cur])
+                    hy[cur].copy_(yout[cur], non_blocking=True)
+                    copied[cur].record()
+                if i >= 1:
+                    copied[nxt].synchronize()             # the host has step i-1's result
+            copied[(k - 1) & 1].synchronize()
+            main.wait_event(copied[(k - 1) & 1])
 
         e2e_loop(2)
         barrier()
@@ -314,9 +330,10 @@ def main():
         e2e = {"value": args.bytes / (e_ms * 1e-3) / 1e9 * factor * world, "unit": "GB/s",
                "busbw_per_gpu": args.bytes / (e_ms * 1e-3) / 1e9 * factor,
                "ms_per_step": e_ms, "wall_ms_per_step": wall_ms / args.steps,
-               "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": count * hy.element_size(),
+               "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": count * hy[0].element_size(),
                "note": "pinned host input uploaded and the full result read back every step; the upload of step "
-                       "i+1 overlaps the collective of step i"}
+                       "i+1, the collective of step i and the read-back of step i-1 overlap (the host waits for "
+                       "each step's result one step later)"}
 
     # ---- the same collective through the LD_PRELOAD interposer and the C benchmark driver ----
     interposed = None
