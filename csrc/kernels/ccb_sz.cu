@@ -45,6 +45,7 @@
 
 #include "../rt/ccb_rt_internal.h"
 #include "ccb/ccb_sz.h"
+#include "ccb_fastdiv.h"
 #include "ccb_reduce.cuh"
 
 namespace cg = cooperative_groups;
@@ -85,9 +86,8 @@ struct SzArgs {
   unsigned int bcast_waves;          // progress steps a broadcast root publishes (1..kMaxBcastWaves)
   unsigned long long slot_bytes;     // arena bytes of one source's slot (ngroups * kGroupStride, rounded)
   // Division of a tile index by tiles_x and by tiles_x * tiles_y as a multiplication:
-  // magic = floor(2^40 / d) + 1 and q = (tile * magic) >> 40, exact for tile < 2^22 and
-  // d < 2^18 (then tile * d < 2^40 and the product fits 64 bits; the host checks the two
-  // limits, 0 = use the division). An integer division by a run-time value
+  // (ccb_fastdiv.h; exact for tile < 2^22 and d < 2^18, which the host checks: 0 = use the
+  // division). An integer division by a run-time value
   // costs about 25 instructions, and every thread needs three per tile.
   unsigned long long magic_x, magic_xy;
 };
@@ -125,9 +125,9 @@ __device__ __forceinline__ TileCoord tile_coord(const SzArgs& a, unsigned int ti
   unsigned int tx, ty, tz;
   if (a.magic_x) {
     const unsigned int txy = a.tiles_x * a.tiles_y;
-    tz = (unsigned int)(((unsigned long long)tile * a.magic_xy) >> 40);
+    tz = ccb_fastdiv(tile, a.magic_xy);
     const unsigned int rem = tile - tz * txy;
-    ty = (unsigned int)(((unsigned long long)rem * a.magic_x) >> 40);
+    ty = ccb_fastdiv(rem, a.magic_x);
     tx = rem - ty * a.tiles_x;
   } else {
     tx = tile % a.tiles_x, ty = (tile / a.tiles_x) % a.tiles_y, tz = tile / (a.tiles_x * a.tiles_y);
@@ -646,12 +646,9 @@ static void fill_geometry(SzArgs& a, int nx, int ny, int nz, float eb) {
   const unsigned long long txy = (unsigned long long)a.tiles_x * a.tiles_y;
   // tile indices run up to ngroups * kClusterSize (the last group may be partly empty)
   const unsigned long long max_tile = (unsigned long long)a.ngroups * kClusterSize;
-  if (max_tile < (1ull << 22) && txy < (1ull << 18)) {
-    a.magic_x = (1ull << 40) / (unsigned long long)a.tiles_x + 1;
-    a.magic_xy = (1ull << 40) / txy + 1;
-  } else {
-    a.magic_x = a.magic_xy = 0;
-  }
+  a.magic_x = ccb_fastdiv_magic(max_tile, (unsigned long long)a.tiles_x);
+  a.magic_xy = ccb_fastdiv_magic(max_tile, txy);
+  if (!a.magic_x || !a.magic_xy) a.magic_x = a.magic_xy = 0;
   a.eb = eb;
   a.two_eb = 2.f * eb * (1.f - 0.0009765625f);  // quantisation step: 2 eb (1 - 2^-10)
   a.inv_two_eb = 1.f / a.two_eb;

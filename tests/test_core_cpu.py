@@ -376,3 +376,34 @@ def test_sixteen_bit_types_through_the_core(core, name, code, npconv):
     core.compute_max_abs_err.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
     err = core.compute_max_abs_err(other, ref, n, code)
     assert 0 < err <= 1.0
+
+
+def test_fast_division_by_a_magic_number_is_exact_in_its_stated_range(tmp_path):
+    """The multiplication that replaces run-time integer divisions in the kernels
+    (csrc/kernels/ccb_fastdiv.h): every numerator below 2^22 for a spread of divisors below
+    2^18, and the refusal outside that range."""
+    import shutil
+    import subprocess
+
+    if not shutil.which("gcc"):
+        pytest.skip("no C compiler")
+    src = tmp_path / "t.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include "ccb_fastdiv.h"
+int main(void) {
+    unsigned long long bad = 0, n_checked = 0;
+    for (unsigned d = 1; d < (1u << 18); d = d < 70 ? d + 1 : d * 3 / 2 + 1) {
+        const uint64_t m = ccb_fastdiv_magic((1u << 22) - 1, d);
+        if (!m) { bad++; continue; }
+        for (uint32_t n = 0; n < (1u << 22); ++n) { n_checked++; if (ccb_fastdiv(n, m) != n / d) bad++; }
+    }
+    if (ccb_fastdiv_magic(1u << 22, 3) || ccb_fastdiv_magic(100, 1u << 18) || ccb_fastdiv_magic(100, 0)) bad++;
+    printf("%llu %llu\n", n_checked, bad);
+    return bad != 0;
+}''')
+    exe = tmp_path / "t"
+    subprocess.run(["gcc", "-O2", "-I" + os.path.join(ROOT, "csrc", "kernels"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout
+    assert int(out.stdout.split()[0]) > 100_000_000
