@@ -17,12 +17,12 @@ def test_reference_arm_at_one_rank_reports_unavailable():
 
 def test_flags_and_defaults():
     out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--help"], capture_output=True, text=True, timeout=120).stdout
-    for flag in ("--gpus", "--steps", "--warmup", "--impl"):
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--via", "--no-call-overlap"):
         assert flag in out
     src = (ROOT / "bench.py").read_text()
     for key in ('"metric"', '"value"', '"unit"', '"n_gpus"', '"steps"', '"warmup"', '"ms_per_step"', '"higher_is_better"', '"scaling"',
                 '"vs_baseline"', '"dtype"', '"data"', '"config"', '"clocks"', '"e2e"', '"gpu_launches"', '"h2d_bytes_per_step"',
-                '"d2h_bytes_per_step"'):
+                '"d2h_bytes_per_step"', '"serialised_ms_per_step"', '"pipelined_kernel"', '"call_overlap"'):
         assert key in src, key
 
 
