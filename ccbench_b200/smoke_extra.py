@@ -86,3 +86,23 @@ def run() -> None:
         assert comm.status()[0] == 0
     finally:
         comm.close()
+    # the link probe (stores and bulk copies into the own arena on a one-rank communicator)
+    # and the integer fold of the NCCL-free provider
+    import ctypes
+    import os
+
+    from ._lib import lib
+    from .comm import _check
+
+    one = Communicator.create(0, 1, f"smoke{os.getpid()}", arena_bytes=64 << 20)
+    try:
+        stream = torch.cuda.current_stream().cuda_stream
+        for method in (0, 2):
+            _check(lib().ccb_link_probe(one._h, method, 0, 8 << 20, stream))
+        parts = torch.arange(3 * 1000, dtype=torch.int32).reshape(3, 1000).to(dev)
+        out = torch.empty(1000, dtype=torch.int32, device=dev)
+        _check(lib().ccb_fold(18, 0, ctypes.c_void_p(parts.data_ptr()), 1000, 3, 1000, ctypes.c_void_p(out.data_ptr()), stream))
+        torch.cuda.synchronize()
+        assert torch.equal(out, parts.sum(0).to(torch.int32)) and one.status()[0] == 0
+    finally:
+        one.close()
