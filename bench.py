@@ -371,15 +371,17 @@ def main():
     factor = 2 * (world - 1) / world if world > 1 else 1.0
     algbw = args.bytes / (ms_per_step * 1e-3) / 1e9
     # roofline of the fused kernel: the wire bytes one GPU must push over NVLink at the
-    # nominal 900 GB/s per direction (a peer copy measures 770 GB/s, SM-issued peer stores
-    # 711 GB/s); one rank: input + output at the measured 6553 GB/s copy bandwidth
+    # nominal 900 GB/s per direction (a copy-engine peer copy measures 770 GB/s, stores issued
+    # by SMs 695 GB/s with traffic both ways: ccbench_b200.bench.linkprobe); one rank: input +
+    # output at the measured 6553 GB/s copy bandwidth
     from ccbench_b200.comm import wire_bytes as _wire_bytes
 
     if world > 1:
         wire = factor * _wire_bytes(args.codec, dtype, count)
         bound_ms = wire / 900e9 * 1e3
         roofline = {"bound": "nvlink", "gbs": 900, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step,
-                    "fraction_of_measured_770": wire / 770e9 * 1e3 / ms_per_step}
+                    "fraction_of_measured_770": wire / 770e9 * 1e3 / ms_per_step,
+                    "fraction_of_sm_store_rate_695": wire / 695e9 * 1e3 / ms_per_step}
     else:
         bound_ms = 2 * args.bytes / 6553e9 * 1e3
         roofline = {"bound": "hbm", "gbs": 6553, "bound_ms": bound_ms, "fraction": bound_ms / ms_per_step}
