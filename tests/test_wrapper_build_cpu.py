@@ -129,3 +129,20 @@ exec gcc -I{ROOT / 'csrc/minimpi'} "$@" {mini} -Wl,-rpath,{mini.parent}
         probe = ROOT / "bin" / "libs" / "libstub_mpicc_probe.so"
         if probe.exists():
             probe.unlink()
+
+
+@pytest.mark.parametrize("folder,symbols", [
+    ("plain_nccl_compress", {"ncclAllReduce", "ncclReduceScatter", "ncclSend", "ncclGroupEnd"}),
+    ("nccl_via_uccl", {"ncclGetUniqueId", "ncclCommInitRank", "ncclAllReduce", "ncclSend", "ncclRecv", "ncclGroupStart"}),
+])
+def test_reference_wrapper_folders_build_in_mode_3(cleanup, folder, symbols):
+    """A configuration that still names the reference's communication-wrapper folders in
+    source_dirs builds the corresponding wrapper of this repository, linked with libccb."""
+    if not (ROOT / "bin/libs/libccb.so").exists():
+        pytest.skip("native side not built (python -m ccbench_b200.cli build)")
+    name = f"libtest_{folder}.so"
+    out = build_wrapper("comm", _sel(3, name, source_dirs=[f"userconfig/wrapper_code_examples/communication/{folder}"]), "nccl")
+    cleanup.append(out)
+    assert out is not None and symbols <= _exports(out)
+    needed = subprocess.run(["readelf", "-d", str(out)], capture_output=True, text=True).stdout
+    assert "libccb.so" in needed
