@@ -42,11 +42,15 @@ def build(verbose: bool = False) -> None:
     if all(p.exists() for p in perf_src):
         nb.cc(libs / "libperfnccl.so", perf_src, shared=True, libs=["-ldl", "-lpthread"], verbose=verbose, compiler="cc")
     # example compression wrapper with its own kernels (4-bit / 8-bit groups, SDP4Bit chunk layout)
-    sdp = root / "userconfig/wrapper_code_examples/compression/sdp4bit/sdp4bit.cu"
-    out = libs / "libsdp4bit.so"
-    if sdp.exists() and nb._newer(out, [sdp]):
-        import shutil
+    import shutil
 
-        nvcc = shutil.which("nvcc") or str(nb.CUDA / "bin" / "nvcc")
-        nb._run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-shared", "-Xcompiler", "-fPIC",
-                 *(f"-I{i}" for i in nb.INC), sdp, "-o", out], verbose)
+    nvcc = shutil.which("nvcc") or str(nb.CUDA / "bin" / "nvcc")
+    for src, name in [
+        (root / "userconfig/wrapper_code_examples/compression/sdp4bit/sdp4bit.cu", "libsdp4bit.so"),
+        # the user template of the four hooks, built with its example codec so that it is tested
+        (root / "userconfig/wrapper_code_examples/compression/coccl_wrapper_template.cu", "libcoccl_wrapper_template.so"),
+    ]:
+        out = libs / name
+        if src.exists() and nb._newer(out, [src]):
+            nb._run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-shared", "-Xcompiler", "-fPIC",
+                     *(f"-I{i}" for i in nb.INC), src, "-o", out], verbose)

@@ -139,3 +139,31 @@ def test_all_chunks_of_a_hook_call_are_one_launch():
     assert torch.equal(out.cpu(), want.float().to(torch.bfloat16))
     # decode and add contract into one fused multiply-add: equal up to one rounding of the 16-bit result
     assert (acc.cpu().float() - (want.float() + 1)).abs().max().item() <= 2.0 ** -7 * (want.abs().max().item() + 1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_user_template_of_the_four_hooks_with_its_example_codec(dtype):
+    """userconfig/wrapper_code_examples/compression/coccl_wrapper_template.cu as shipped (fp16
+    values relative to a per-group absmax): round trip, decode + add, and the one-pass sum of
+    all chunks re-encoded, every hook one launch for all chunks; odd chunk length."""
+    L = _load("libcoccl_wrapper_template.so")
+    chunks, per = 5, 4096 + 37
+    x = torch.randn(chunks * per, generator=torch.Generator().manual_seed(5)).to(dtype).cuda()
+    comp, stride, per = _compress(L, x, chunks)
+    assert stride < per * 4 and stride % 16 == 0
+    out = torch.empty_like(x)
+    assert L.ncclDecompress(out.data_ptr(), comp.data_ptr(), per, DT[dtype], stride, NCCL_U8, chunks, 2, _stream()) == 0
+    tol = 2e-3 if dtype == torch.float32 else 1.2e-2
+    ref = x.float()
+    assert ((out.float() - ref).abs() <= tol * ref.abs().view(chunks, per).amax(1, keepdim=True).expand(chunks, per).reshape(-1) + 1e-6).all()
+    acc = torch.ones_like(x)
+    assert L.ncclDecompressReduce(acc.data_ptr(), comp.data_ptr(), stride, NCCL_U8, per, DT[dtype], chunks, 2, _stream()) == 0
+    assert torch.allclose(acc.float(), out.float() + 1, rtol=1e-2, atol=1e-2)
+    p, rc, rd = ctypes.c_void_p(None), ctypes.c_size_t(0), ctypes.c_int(-1)
+    assert L.ncclDecompReduceComp(comp.data_ptr(), ctypes.byref(p), per, DT[dtype], stride, NCCL_U8, ctypes.byref(rc), ctypes.byref(rd),
+                                  chunks, 2, _stream()) == 0
+    one = torch.empty(per, dtype=dtype, device="cuda")
+    assert rc.value == stride and L.ncclDecompress(one.data_ptr(), p, per, DT[dtype], rc.value, NCCL_U8, 1, 2, _stream()) == 0
+    torch.cuda.synchronize()
+    total = out.float().view(chunks, per).sum(0)
+    assert (one.float() - total).abs().max().item() <= 1.5e-2 * total.abs().max().item()
