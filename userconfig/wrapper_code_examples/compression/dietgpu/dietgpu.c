@@ -17,21 +17,15 @@
 #include <nccl.h>
 #include <stdint.h>
 
-#include "ccb/ccb.h"
-#include "ccb/ccb_lossless.h"
+#include "dietgpu_common.h"
 
 typedef enum {
     AlltoAll = 0, AlltoAll_Inter = 1, AllReduce = 2, AllReduce_Inter = 3, AllGather = 4, AllGather_Inter = 5,
     ReduceScatter = 6, ReduceScatter_Inter = 7, SendRecv = 8, SendRecv_BWD = 9
 } ncclCommOp_t;
 
-static int hook_dtype(ncclDataType_t t) {
-    if (t == ncclFloat32) return CCB_F32;
-    if (t == ncclFloat16) return CCB_F16;
-    if ((int)t == 9) return CCB_BF16;
-    return -1;
-}
-static size_t esz(int dt) { return dt == CCB_F32 ? 4 : 2; }
+static int hook_dtype(ncclDataType_t t) { return lossless_dtype_of(t); }
+static size_t esz(int dt) { return lossless_elem_bytes(dt); }
 
 size_t ncclCompressedChunkBytes(size_t chunkCount, ncclDataType_t datatype) {
     const int dt = hook_dtype(datatype);
