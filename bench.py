@@ -282,7 +282,9 @@ def main():
         done = [torch.cuda.Event(), torch.cuda.Event()]
         copied = [torch.cuda.Event(), torch.cuda.Event()]
 
-        def e2e_loop(k, duplex=True):
+        hm = [torch.empty(1, dtype=torch.float32).pin_memory(), torch.empty(1, dtype=torch.float32).pin_memory()]
+
+        def e2e_loop(k, duplex=True, full=True):
             # Three stages in flight: the upload of step i+1, the collective of step i and the
             # read-back of step i-1 (two device buffers each way). The host waits for the
             # result of step i-1 while step i runs, and for the last one at the end.
@@ -307,9 +309,14 @@ def main():
                 comm.all_reduce(xin[cur], yout[cur], codec=args.codec, algo=args.algo, error_feedback=ef)
                 freed[cur].record()
                 done[cur].record()
-                with torch.cuda.stream(back):
-                    back.wait_event(done[cur])
-                    hy[cur].copy_(yout[cur], non_blocking=True)
+                if full:
+                    with torch.cuda.stream(back):
+                        back.wait_event(done[cur])
+                        hy[cur].copy_(yout[cur], non_blocking=True)
+                        copied[cur].record()
+                else:   # a metric of the result (its squared norm) instead of the result itself
+                    metric = yout[cur].float().square().sum().reshape(1)
+                    hm[cur].copy_(metric, non_blocking=True)
                     copied[cur].record()
                 if i >= 1:
                     copied[nxt].synchronize()             # the host has step i-1's result
@@ -344,11 +351,28 @@ def main():
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e_ms = te.item() / args.steps
+        # the same loop reading back a 4-byte metric of the result instead of the result: what
+        # the upload and the collective cost without the second PCIe stream
+        e2e_loop(2, duplex, False)
+        metric_ms = 0.0
+        barrier()
+        ms0, ms1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ms0.record()
+        e2e_loop(args.steps, duplex, False)
+        ms1.record()
+        barrier()
+        tm = torch.tensor([ms0.elapsed_time(ms1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        metric_ms = tm.item() / args.steps
         factor = 2 * (world - 1) / world if world > 1 else 1.0
         e2e = {"value": args.bytes / (e_ms * 1e-3) / 1e9 * factor * world, "unit": "GB/s",
                "busbw_per_gpu": args.bytes / (e_ms * 1e-3) / 1e9 * factor,
                "ms_per_step": e_ms, "wall_ms_per_step": wall_ms / args.steps,
                "h2d_bytes_per_step": args.bytes, "d2h_bytes_per_step": count * hy[0].element_size(),
+               "metric_readback": {"ms_per_step": metric_ms, "d2h_bytes_per_step": 4,
+                                   "value": args.bytes / (metric_ms * 1e-3) / 1e9 * factor * world,
+                                   "note": "the same loop with the squared norm of the result read back instead of the result"},
                "copy_schedule": ("uploads and read-backs at once (two copy streams)" if duplex else
                                  "one PCIe direction at a time (one copy stream)"),
                "copy_schedule_trial_ms": {"both_directions_at_once": trial[True], "one_direction_at_a_time": trial[False]},
