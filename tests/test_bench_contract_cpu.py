@@ -22,7 +22,8 @@ def test_flags_and_defaults():
     src = (ROOT / "bench.py").read_text()
     for key in ('"metric"', '"value"', '"unit"', '"n_gpus"', '"steps"', '"warmup"', '"ms_per_step"', '"higher_is_better"', '"scaling"',
                 '"vs_baseline"', '"dtype"', '"data"', '"config"', '"clocks"', '"e2e"', '"gpu_launches"', '"h2d_bytes_per_step"',
-                '"d2h_bytes_per_step"', '"serialised_ms_per_step"', '"pipelined_kernel"', '"call_overlap"'):
+                '"d2h_bytes_per_step"', '"serialised_ms_per_step"', '"pipelined_kernel"', '"call_overlap"', '"metric_readback"', '"copy_schedule"',
+                '"fraction_of_sm_store_rate_695"'):
         assert key in src, key
 
 
